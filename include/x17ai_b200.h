@@ -1,0 +1,307 @@
+/*
+ * C ABI of libx17ai_b200.so: the B200 (sm_100a) drop-in for the quantized block-forward
+ * hot path of x17ai.
+ *
+ * Part 1 re-exports, with identical names, argument lists, struct layouts and ownership
+ * rules, the 21 functions of the reference's driver shim (cpp/cuda_shim.cpp:189-988,
+ * declared for the Rust host in src/device/cuda/cuda_shim.rs:76-158).
+ *
+ * Part 2 adds one entry point per hot-path kernel.  In the reference these kernels are
+ * rendered from templates, compiled by nvcc at run time into one cubin per shape and
+ * launched through x17ai_cuda_launch_kernel; here they are precompiled for sm_100a and
+ * take their shapes and scales at run time, so the Rust launchers
+ * (src/device/cuda/attn.rs, gemm.rs) call one function instead of render + nvcc + load +
+ * launch.  Every entry point follows the shim's conventions: it returns a
+ * DiagnosticBuffer* that is NULL on success and otherwise owned by the caller until it is
+ * handed, once, to x17ai_move_diagnostic; all work is enqueued on the given stream and
+ * nothing is synchronised; no CUDA context is left current on the calling thread.
+ */
+#ifndef X17AI_B200_H
+#define X17AI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Part 1: the reference shim (cpp/ffi.hpp, cpp/cuda_shim.cpp)
+ * ---------------------------------------------------------------------------------------- */
+
+/* cpp/ffi.hpp:12-23; Rust side src/util/ffi_buffer.rs:14-103 */
+typedef struct x17ai_FfiSpan {
+	char *ptr;
+	size_t len;
+} x17ai_FfiSpan;
+
+typedef struct x17ai_FfiBufferVMT {
+	x17ai_FfiSpan (*span)(void *self);
+	x17ai_FfiSpan (*buf_span)(void *self);
+	x17ai_FfiSpan (*extend)(void *self, size_t additional);
+	void (*clear)(void *self);
+	void (*set_len)(void *self, size_t new_len);
+} x17ai_FfiBufferVMT;
+
+typedef struct x17ai_FfiBuffer {
+	void *instance;
+	x17ai_FfiBufferVMT const *vmt;
+} x17ai_FfiBuffer;
+
+/* cpp/ffi.hpp:84-93: opaque to the caller */
+typedef struct x17ai_DiagnosticBuffer x17ai_DiagnosticBuffer;
+
+/* cpp/cuda_shim.cpp:56-63; the Rust host reads only the first field (cuda_shim.rs:20-24) */
+typedef struct x17ai_CudaContextHandle {
+	size_t refcnt_munus_one;
+	size_t device_id;
+	size_t capability_major;
+	size_t capability_minor;
+	size_t warp_size;
+	int device;    /* CUdevice */
+	void *context; /* CUcontext */
+} x17ai_CudaContextHandle;
+
+typedef struct x17ai_CudaStreamHandle x17ai_CudaStreamHandle; /* is a CUstream   (cuda_shim.cpp:385) */
+typedef struct x17ai_CudaModuleHandle x17ai_CudaModuleHandle; /* is a CUmodule   (cuda_shim.cpp:826) */
+typedef struct x17ai_CudaKernelHandle x17ai_CudaKernelHandle; /* is a CUfunction (cuda_shim.cpp:903) */
+typedef struct x17ai_CudaDeviceData x17ai_CudaDeviceData;     /* is a CUdeviceptr (cuda_shim.cpp:83-93) */
+typedef struct x17ai_CudaTimerHandle x17ai_CudaTimerHandle;   /* cuda_shim.cpp:76-81 */
+
+/* cpp/cuda_shim.cpp:64-74 */
+typedef struct x17ai_CudaKernelAttrs {
+	int32_t max_threads_per_block;
+	int32_t static_shared_size_bytes;
+	int32_t const_size_bytes;
+	int32_t local_size_bytes;
+	int32_t num_regs;
+	int32_t ptx_version;
+	int32_t binary_version;
+	int32_t max_dynamic_shared_size_bytes;
+	int32_t preferred_shared_memory_carveout;
+} x17ai_CudaKernelAttrs;
+
+/* PtrResult<T> (cpp/ffi.hpp:161-175): returned by value, two pointers */
+#define X17AI_PTR_RESULT(T, NAME)            \
+	typedef struct NAME {                    \
+		T *value;                            \
+		x17ai_DiagnosticBuffer *diagnostic;  \
+	} NAME
+X17AI_PTR_RESULT(x17ai_CudaContextHandle, x17ai_ContextResult);
+X17AI_PTR_RESULT(x17ai_CudaStreamHandle, x17ai_StreamResult);
+X17AI_PTR_RESULT(x17ai_CudaTimerHandle, x17ai_TimerResult);
+X17AI_PTR_RESULT(x17ai_CudaDeviceData, x17ai_DeviceDataResult);
+X17AI_PTR_RESULT(x17ai_CudaModuleHandle, x17ai_ModuleResult);
+X17AI_PTR_RESULT(x17ai_CudaKernelHandle, x17ai_KernelResult);
+
+/* cuda_shim.cpp:190-205 */
+void x17ai_move_diagnostic(x17ai_DiagnosticBuffer *diag, x17ai_FfiBuffer err);
+/* cuda_shim.cpp:207-317 */
+x17ai_ContextResult x17ai_cuda_open_context(size_t device_id);
+/* cuda_shim.cpp:319-341 */
+x17ai_DiagnosticBuffer *x17ai_cuda_close_context(x17ai_CudaContextHandle *context);
+/* cuda_shim.cpp:343-347 */
+void *x17ai_cuda_context_ptr(x17ai_CudaContextHandle *context);
+/* cuda_shim.cpp:349-387 */
+x17ai_StreamResult x17ai_cuda_open_stream(x17ai_CudaContextHandle *ctx);
+/* cuda_shim.cpp:389-408 */
+x17ai_DiagnosticBuffer *x17ai_cuda_close_stream(x17ai_CudaStreamHandle *stream);
+/* cuda_shim.cpp:410-430 */
+x17ai_DiagnosticBuffer *x17ai_cuda_synchronize(x17ai_CudaStreamHandle *stream);
+/* cuda_shim.cpp:432-503 */
+x17ai_TimerResult x17ai_cuda_create_timer(x17ai_CudaContextHandle *context, x17ai_CudaStreamHandle *stream);
+/* cuda_shim.cpp:505-562 */
+x17ai_DiagnosticBuffer *x17ai_cuda_destroy_timer(x17ai_CudaTimerHandle *timer);
+/* cuda_shim.cpp:564-581 */
+x17ai_DiagnosticBuffer *x17ai_cuda_timer_start(x17ai_CudaTimerHandle *timer);
+/* cuda_shim.cpp:583-600 */
+x17ai_DiagnosticBuffer *x17ai_cuda_timer_stop(x17ai_CudaTimerHandle *timer);
+/* cuda_shim.cpp:602-652 */
+x17ai_DiagnosticBuffer *x17ai_cuda_timer_elapsed_seconds(x17ai_CudaTimerHandle *timer, double *seconds);
+/* cuda_shim.cpp:654-679 */
+x17ai_DeviceDataResult x17ai_cuda_alloc(x17ai_CudaStreamHandle *stream, size_t bytes);
+/* cuda_shim.cpp:681-700 */
+x17ai_DiagnosticBuffer *x17ai_cuda_free(x17ai_CudaStreamHandle *stream, x17ai_CudaDeviceData *ptr);
+/* cuda_shim.cpp:702-733 */
+x17ai_DiagnosticBuffer *x17ai_cuda_upload_data(x17ai_CudaStreamHandle *stream, uint8_t const *src,
+											   x17ai_CudaDeviceData *dst, size_t offset_bytes, size_t size_bytes);
+/* cuda_shim.cpp:735-766 */
+x17ai_DiagnosticBuffer *x17ai_cuda_download_data(x17ai_CudaStreamHandle *stream, x17ai_CudaDeviceData *src,
+												 uint8_t *dst, size_t offset_bytes, size_t size_bytes);
+/* cuda_shim.cpp:768-828 */
+x17ai_ModuleResult x17ai_cuda_load_module(x17ai_CudaContextHandle *ctx, char const *cubin_path);
+/* cuda_shim.cpp:830-846 */
+x17ai_DiagnosticBuffer *x17ai_cuda_del_module(x17ai_CudaModuleHandle *module);
+/* cuda_shim.cpp:848-905 */
+x17ai_KernelResult x17ai_cuda_get_kernel(x17ai_CudaModuleHandle *module, char const *name, size_t smem_size);
+/* cuda_shim.cpp:907-927 */
+x17ai_DiagnosticBuffer *x17ai_cuda_read_kernel_attrs(x17ai_CudaKernelHandle *kernel, x17ai_CudaKernelAttrs *attrs);
+/* cuda_shim.cpp:929-987 */
+x17ai_DiagnosticBuffer *x17ai_cuda_launch_kernel(x17ai_CudaStreamHandle *stream, x17ai_CudaKernelHandle *kernel,
+												 size_t grid_x, size_t grid_y, size_t grid_z,
+												 size_t block_x, size_t block_y, size_t block_z,
+												 size_t shared_mem_bytes, void **args);
+
+/* ------------------------------------------------------------------------------------------
+ * Part 2: hot-path kernels
+ * ---------------------------------------------------------------------------------------- */
+
+/* DType codes of the Rust host (src/dtype.rs:3-8) */
+enum {
+	X17AI_DTYPE_E4M3 = 0x30,
+	X17AI_DTYPE_INT8 = 0x31,
+	X17AI_DTYPE_BF16 = 0x40,
+	X17AI_DTYPE_F32 = 0x50,
+	X17AI_DTYPE_I32_RAW = 0x51 /* validation only: raw 32-bit accumulators as GEMM output */
+};
+
+/* AttnKernelConfig (src/device/cuda/attn.rs:45-53); dtype is always Int8.
+ * Strides are in elements (bytes) per sequence position. */
+typedef struct x17ai_AttnConfig {
+	size_t n_heads;
+	size_t head_dim; /* 32, 64 or 128 */
+	size_t q_stride;
+	size_t kv_stride;
+	size_t o_stride;
+} x17ai_AttnConfig;
+
+/* Launch metadata the reference reads from meta.json (attn.rs:311-316) */
+typedef struct x17ai_AttnMeta {
+	size_t threads_per_block;
+	size_t smem_bytes;
+	size_t q_per_block;
+} x17ai_AttnMeta;
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_meta(x17ai_AttnConfig const *cfg, x17ai_AttnMeta *meta);
+
+/*
+ * int8 sliding-window attention forward.  Replaces AttnKernel::launch
+ * (src/device/cuda/attn.rs:353-447) and the kernel it launches
+ * (templates/attn/kernel.cu:9-33 -> AttnForward::run, cuda/attn_fwd_i8.cuh:368-619).
+ *   q   [batch][seq_len][q_stride]  int8 FixedI8, head h at columns h*D .. h*D+D-1
+ *   kv  [batch][seq_len][kv_stride] int8, head h at columns 2*h*D: [K(D) | V(D)]
+ *   sink_k, sink_v [n_heads][D] int8;  attn_temperature [n_heads] f32
+ *   out [batch][seq_len][o_stride] int8;  l [batch][n_heads][seq_len] f32 or NULL
+ *   window_size: 0 = unbounded, else a multiple of 16 (attn.rs:405-410)
+ * batch = 1 is the reference's call; batch > 1 runs independent sequences laid out back to
+ * back in one launch.  seq_len need not be a multiple of the query tile.
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size);
+
+/* Same launch with validation outputs: dbg_s int32 [batch*n_heads][seq][seq] raw scores of the
+ * visited tiles, dbg_p uint8 [batch*n_heads][seq][seq] quantised probabilities, dbg_o int32
+ * [batch*n_heads][seq][D] the int32 P.V accumulator.  Small shapes only. */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_debug(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size,
+	int32_t *dbg_s, uint8_t *dbg_p, int32_t *dbg_o);
+
+/*
+ * int8 decode attention: one new token per sequence at position kv_len against an int8 KV
+ * cache.  The reference names attn_incremental (attn_incremental.cu:329-481) but ships no
+ * int8 decode; semantics are those of row kv_len of x17ai_b200_attn_fwd_i8.
+ *   q [batch][q_stride]; kv_cache [batch][kv_capacity][kv_stride]; kv_lens [batch] or NULL
+ *   (then every sequence has kv_len cached tokens); out [batch][o_stride]; l [batch][n_heads]
+ *   or NULL.
+ * When batch*n_heads is too small to fill the GPU the keys are split over several CTAs and
+ * the partial results pass through stream-ordered scratch memory that this call allocates
+ * and frees (cudaMallocAsync / cudaFreeAsync on `stream`).
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
+	int8_t const *q, int8_t const *kv_cache, size_t kv_capacity, size_t kv_len,
+	uint32_t const *kv_lens, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, size_t n_splits);
+
+/* Epilogues of the GEMM (src/device/cuda/gemm.rs: ScaleEpilogue :60-110, RMSNormEpilogue
+ * :112-166, ResidualEpilogue :168-212, GeGluEpilogue :214-255) */
+enum {
+	X17AI_EPILOGUE_SCALE = 0,
+	X17AI_EPILOGUE_RMS_NORM = 1,
+	X17AI_EPILOGUE_GEGLU = 2,
+	X17AI_EPILOGUE_RESIDUAL = 3
+};
+
+/* GemmConfig + epilogue config (gemm.rs:257-366).  B is always given transposed, i.e. as
+ * [b_rows][a_cols] row-major (gemm.rs:462-467). */
+typedef struct x17ai_GemmConfig {
+	int32_t a_dtype; /* INT8 or E4M3 */
+	int32_t b_dtype; /* INT8, or E4M3 (standard OCP e4m3 x e4m3 tensor-core mode) */
+	int32_t c_dtype; /* INT8 or E4M3 (or I32_RAW with the SCALE epilogue) */
+	int32_t epilogue;
+	size_t a_cols;   /* K */
+	size_t b_rows;   /* N_raw */
+	double inp_scale;
+	double out_scale;
+	double eps;      /* RMS_NORM */
+	size_t head_dim; /* RMS_NORM: raw columns per head are [K(head_dim) | V(head_dim)] */
+} x17ai_GemmConfig;
+
+/* Launch metadata the reference reads from meta.json (gemm.rs:531-537) */
+typedef struct x17ai_GemmMeta {
+	size_t threads_per_block;
+	size_t smem_bytes;
+	size_t m_per_block;
+	size_t n_per_block;
+} x17ai_GemmMeta;
+
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_meta(x17ai_GemmConfig const *cfg, x17ai_GemmMeta *meta);
+
+/*
+ * Fused GEMM.  Replaces GemmKernel<E>::launch (gemm.rs:439-443, 591-641) and the kernels
+ * rendered from templates/basic_gemm/kernel.cu:9-32 (b8::Gemm, cuda/gemm_b8.cuh:666-754;
+ * b16::Gemm, cuda/gemm_b16.cuh:478-566).
+ *   a [a_rows][a_cols]; b [b_rows][a_cols]; c [a_rows][b_rows] (SCALE, RMS_NORM) or
+ *   [a_rows][b_rows/2] (GEGLU, RESIDUAL); rrms f32 [a_rows][b_rows / (2*head_dim)] (RMS_NORM);
+ *   residual int8 [a_rows][b_rows/2] (RESIDUAL).
+ * a_dtype E4M3 with b_dtype INT8 (the reference's ffn_y_fwd_f8) needs b in the split form
+ * produced by x17ai_b200_split_i8_weights: pass that buffer as b.
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
+	x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
+	void const *a, size_t a_rows, void const *b, size_t b_rows,
+	void *c, float *rrms, int8_t const *residual);
+
+/* One-time weight preparation for e4m3 activations x int8 weights: writes
+ * out[rows][2*cols] e4m3 = [16*hi | lo] with w = 16*hi + lo, hi in [-8, 8], lo in [0, 15],
+ * both exactly representable in e4m3, so that A.[16*hi|lo]^T with A repeated along K equals
+ * A.W^T exactly term by term. */
+x17ai_DiagnosticBuffer *x17ai_b200_split_i8_weights(
+	x17ai_CudaStreamHandle *stream, int8_t const *w, size_t rows, size_t cols, uint8_t *out);
+
+/* RMSNorm modes */
+enum {
+	X17AI_RMS_E4M3_FIXED = 0,   /* e4m3 in, FixedI8 out: Rms_norm::kernel (rms_norm.cu:55-113) */
+	X17AI_RMS_BF16_FIXED = 1,   /* bf16 in, FixedI8 out */
+	X17AI_RMS_BF16_ROWSCALE = 2 /* bf16 in, int8 out + f32 per-row absmax/127 scale */
+};
+
+/* Replaces Rms_norm::kernel (rms_norm.cu:55-113): inp [rows][cols] -> out int8 [rows][cols]. */
+x17ai_DiagnosticBuffer *x17ai_b200_rms_norm(
+	x17ai_CudaStreamHandle *stream, int32_t mode, void const *inp, size_t rows, size_t cols,
+	int8_t *out, float *row_scale, double eps);
+
+/* Device-side status of the kernels launched so far on the stream's device: synchronises the
+ * stream, copies the four status words (0 = ok; else code << 16 | detail of the first bounded
+ * wait that ran out, the reporting block, the number of reports, reserved) and clears them. */
+x17ai_DiagnosticBuffer *x17ai_b200_read_status(x17ai_CudaStreamHandle *stream, uint32_t status[4]);
+
+/* For hosts that cannot build the FfiBuffer callback table (its callbacks return a struct by
+ * value): moves the diagnostic into dst (at most cap bytes, no terminator) through
+ * x17ai_move_diagnostic and a fixed-capacity FfiBuffer, releases it, and returns the number of
+ * bytes written.  diag may be NULL (returns 0). */
+size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_t cap);
+
+/* Number of kernel launches this library has issued since it was loaded (all entry points). */
+uint64_t x17ai_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* X17AI_B200_H */

@@ -1,0 +1,7 @@
+"""CPU oracle for the quantized block-forward hot path.
+
+TEST INFRASTRUCTURE ONLY.  Everything under this package is a checker: the tests, the
+smoke check and the CPU-baseline leg of the benchmark import it; the product path
+(`x17ai_b200`) never does and fails loudly when its CUDA library is missing.
+"""
+from . import attn, formats, gemm, rms_norm  # noqa: F401

@@ -1,0 +1,48 @@
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU; run with -m gpu")
+
+
+def pytest_collection_modifyitems(config, items):
+    # the shared library is built once for the whole session (cross-compiles without a GPU)
+    from x17ai_b200 import build
+    build.build()
+
+
+@pytest.fixture(scope="session")
+def lib():
+    from x17ai_b200 import _lib
+    return _lib.load()
+
+
+@pytest.fixture()
+def stream():
+    """A stream opened through the C ABI; after the test, no kernel may have given up a wait."""
+    from x17ai_b200 import device
+    s = device.CudaStream(0)
+    yield s
+    status = s.read_status()
+    s.close()
+    assert status == [0, 0, 0, 0], f"device status words after the test: {status}"
+
+
+def load_golden(name):
+    g = np.load(GOLDEN / f"{name}.npz")
+    seq, dm, hd, nh, fw, win = [int(v) for v in g["config"]]
+    return g, dict(S=seq, Dm=dm, D=hd, H=nh, F=fw, W=win)
+
+
+def code_hist(a, b):
+    d = np.abs(a.astype(np.int32) - b.astype(np.int32))
+    return np.bincount(d.ravel(), minlength=8)

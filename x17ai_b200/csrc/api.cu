@@ -1,0 +1,706 @@
+// Kernel entry points of libx17ai_b200.so (part 2 of include/x17ai_b200.h): argument checks in
+// the manner of the Rust launchers (src/device/cuda/tensor_check.rs, attn.rs:353-447,
+// gemm.rs:591-641), TMA tensor maps, launch configuration, launches.
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdint>
+#include <mutex>
+
+#include "attn.cuh"
+#include "decode.cuh"
+#include "diag.hpp"
+#include "gemm.cuh"
+#include "rms_norm.cuh"
+
+using x17::make_diag;
+using x17::static_diag;
+
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+
+// ---- per-device state -----------------------------------------------------------------------
+
+constexpr int MAX_DEVICES = 32;
+struct DeviceState {
+	std::once_flag once;
+	uint32_t *status = nullptr;  // 4 words of device memory
+	int sm_count = 0;
+	cudaError_t init_err = cudaSuccess;
+};
+DeviceState g_dev[MAX_DEVICES];
+
+// Makes the stream's context current for the scope (the callers of this library keep no
+// context current, cpp/ffi.hpp:195-206) and resolves the device ordinal.
+struct StreamScope {
+	CUcontext ctx = nullptr;
+	int device = -1;
+	bool pushed = false;
+	x17ai_DiagnosticBuffer *diag = nullptr;
+
+	explicit StreamScope(x17ai_CudaStreamHandle *stream, char const *who) {
+		if (stream == nullptr) {
+			diag = make_diag("x17ai_b200: null stream", who, ": null stream");
+			return;
+		}
+		if (!x17::driver().ok) {
+			diag = make_diag("x17ai_b200: CUDA driver not available", who,
+							 ": the CUDA driver is not available on this machine (", x17::driver().missing,
+							 " not found); this library has no CPU path");
+			return;
+		}
+		CUresult e = DRV(cuStreamGetCtx)(reinterpret_cast<CUstream>(stream), &ctx);
+		if (e == CUDA_SUCCESS) e = DRV(cuCtxPushCurrent)(ctx);
+		if (e != CUDA_SUCCESS) {
+			diag = make_diag("x17ai_b200: cannot enter the stream's context", who,
+							 ": cannot enter the stream's context: ", x17::cu_error_text(e));
+			return;
+		}
+		pushed = true;
+		CUdevice dev;
+		e = DRV(cuCtxGetDevice)(&dev);
+		if (e != CUDA_SUCCESS || int(dev) < 0 || int(dev) >= MAX_DEVICES) {
+			diag = make_diag("x17ai_b200: cannot resolve the device", who, ": cannot resolve the device");
+			return;
+		}
+		device = int(dev);
+		DeviceState &st = g_dev[device];
+		std::call_once(st.once, [&] {
+			int major = 0, minor = 0;
+			cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+			cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+			if (major != 10) {
+				st.init_err = cudaErrorNoKernelImageForDevice;
+				return;
+			}
+			cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device);
+			st.init_err = cudaMalloc(&st.status, 4 * sizeof(uint32_t));
+			if (st.init_err == cudaSuccess) st.init_err = cudaMemset(st.status, 0, 4 * sizeof(uint32_t));
+		});
+		if (st.init_err != cudaSuccess) {
+			diag = make_diag("x17ai_b200: device initialisation failed", who,
+							 ": device initialisation failed (this library needs an sm_100 GPU): ",
+							 cudaGetErrorString(st.init_err));
+		}
+	}
+	~StreamScope() {
+		if (pushed) {
+			CUcontext popped = nullptr;
+			DRV(cuCtxPopCurrent)(&popped);
+		}
+	}
+	DeviceState &state() const { return g_dev[device]; }
+};
+
+x17ai_DiagnosticBuffer *launch_result(char const *who) {
+	cudaError_t e = cudaGetLastError();
+	if (e != cudaSuccess) {
+		return make_diag("x17ai_b200: kernel launch failed", who, ": kernel launch failed: ",
+						 cudaGetErrorString(e));
+	}
+	g_launches.fetch_add(1, std::memory_order_relaxed);
+	return nullptr;
+}
+
+// ---- TMA tensor maps ---------------------------------------------------------------------------
+
+CUtensorMapSwizzle swizzle_for(uint32_t inner_bytes) {
+	return inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+		   : inner_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+							   : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+
+// Byte tensor [d2][d1][d0] (d0 innermost) with row pitch s1 and plane pitch s2, box b0 x b1 x 1.
+CUresult make_map_3d(CUtensorMap *map, void const *base, uint64_t d0, uint64_t d1, uint64_t d2,
+					 uint64_t s1, uint64_t s2, uint32_t b0, uint32_t b1) {
+	cuuint64_t dims[3] = {d0, d1, d2};
+	cuuint64_t strides[2] = {s1, s2};
+	cuuint32_t box[3] = {b0, b1, 1};
+	cuuint32_t estr[3] = {1, 1, 1};
+	return DRV(cuTensorMapEncodeTiled)(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims,
+								  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(b0),
+								  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+CUresult make_map_2d(CUtensorMap *map, void const *base, uint64_t d0, uint64_t d1, uint64_t s1,
+					 uint32_t b0, uint32_t b1) {
+	cuuint64_t dims[2] = {d0, d1};
+	cuuint64_t strides[1] = {s1};
+	cuuint32_t box[2] = {b0, b1};
+	cuuint32_t estr[2] = {1, 1};
+	return DRV(cuTensorMapEncodeTiled)(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims,
+								  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(b0),
+								  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+bool aligned16(void const *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- attention ---------------------------------------------------------------------------------
+
+x17ai_DiagnosticBuffer *check_attn_config(x17ai_AttnConfig const *cfg, char const *who) {
+	if (cfg == nullptr) return make_diag("x17ai_b200: null config", who, ": null config");
+	if (cfg->n_heads == 0) {
+		return make_diag("x17ai_b200: bad attention config", who, ": attention kernel config requires n_heads > 0");
+	}
+	if (cfg->head_dim != 32 && cfg->head_dim != 64 && cfg->head_dim != 128) {
+		return make_diag("x17ai_b200: bad attention config", who,
+						 ": attention kernel config requires head_dim 32, 64 or 128, got ", cfg->head_dim);
+	}
+	size_t const q_cols = cfg->n_heads * cfg->head_dim;
+	if (cfg->q_stride < q_cols) {
+		return make_diag("x17ai_b200: bad attention config", who,
+						 ": attention kernel config requires q_stride >= n_heads * head_dim, got ",
+						 cfg->q_stride, " vs ", q_cols);
+	}
+	if (cfg->kv_stride < 2 * q_cols) {
+		return make_diag("x17ai_b200: bad attention config", who,
+						 ": attention kernel config requires kv_stride >= 2 * n_heads * head_dim, got ",
+						 cfg->kv_stride, " vs ", 2 * q_cols);
+	}
+	if (cfg->o_stride < q_cols) {
+		return make_diag("x17ai_b200: bad attention config", who,
+						 ": attention kernel config requires o_stride >= n_heads * head_dim, got ",
+						 cfg->o_stride, " vs ", q_cols);
+	}
+	if (cfg->q_stride % 16 != 0 || cfg->kv_stride % 16 != 0 || cfg->o_stride % 16 != 0) {
+		return make_diag("x17ai_b200: bad attention config", who,
+						 ": attention strides must be multiples of 16 bytes");
+	}
+	return nullptr;
+}
+
+uint32_t rounded_window(size_t window_size, size_t seq_len) {
+	if (window_size == 0) return 0xFFFFFFFFu;
+	size_t const w = ((window_size - 1) / 16 + 1) * 16;  // cuda/attn_fwd_i8.cuh:408-412
+	return w >= seq_len ? 0xFFFFFFFFu : uint32_t(w);
+}
+
+template <bool DEBUG>
+x17ai_DiagnosticBuffer *attn_launch(
+	char const *who, x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
+	size_t seq_len, int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *temperature, int8_t *out, float *l, size_t window_size, int32_t *dbg_s,
+	uint8_t *dbg_p, int32_t *dbg_o) {
+	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (batch == 0 || seq_len == 0) {
+		return make_diag("x17ai_b200: empty attention input", who, ": attention input q has zero size");
+	}
+	if (seq_len >= (size_t(1) << 31) || batch > 65535 || cfg->n_heads > 65535) {
+		return make_diag("x17ai_b200: attention shape out of range", who, ": attention shape out of range");
+	}
+	if (window_size > 0 && window_size % 16 != 0) {
+		return make_diag("x17ai_b200: bad window", who,
+						 ": attention window_size must be zero or divisible by 16, got ", window_size);
+	}
+	if (!q || !kv || !sink_k || !sink_v || !temperature || !out) {
+		return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	}
+	if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || !aligned16(sink_k) || !aligned16(sink_v)) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+
+	uint32_t const d = uint32_t(cfg->head_dim);
+	CUtensorMap tm_q, tm_kv;
+	CUresult e = make_map_3d(&tm_q, q, cfg->n_heads * d, seq_len, batch, cfg->q_stride,
+							 cfg->q_stride * seq_len, d, x17::attn_cfg::BQ);
+	if (e == CUDA_SUCCESS) {
+		e = make_map_3d(&tm_kv, kv, 2 * cfg->n_heads * d, seq_len, batch, cfg->kv_stride,
+						cfg->kv_stride * seq_len, d, x17::attn_cfg::BKV);
+	}
+	if (e != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
+						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
+	}
+	x17::AttnParams p{};
+	p.seq_len = uint32_t(seq_len);
+	p.n_heads = uint32_t(cfg->n_heads);
+	p.window = rounded_window(window_size, seq_len);
+	p.q = q;
+	p.q_stride = cfg->q_stride;
+	p.q_batch_stride = cfg->q_stride * seq_len;
+	p.sink_k = sink_k;
+	p.sink_v = sink_v;
+	p.temperature = temperature;
+	p.out = out;
+	p.o_stride = cfg->o_stride;
+	p.o_batch_stride = cfg->o_stride * seq_len;
+	p.l = l;
+	p.l_batch_stride = cfg->n_heads * seq_len;
+	p.status = scope.state().status;
+	p.dbg_s = dbg_s;
+	p.dbg_p = dbg_p;
+	p.dbg_o = dbg_o;
+
+	dim3 grid(unsigned((seq_len + x17::attn_cfg::BQ - 1) / x17::attn_cfg::BQ), unsigned(cfg->n_heads),
+			  unsigned(batch));
+	dim3 block(x17::attn_cfg::THREADS);
+	auto go = [&](auto kernel, uint32_t smem) -> cudaError_t {
+		// at least 80 KB so that no more than two CTAs (2 x 256 TMEM columns) share an SM
+		smem = smem < 80u * 1024u ? 80u * 1024u : smem;
+		cudaError_t ce = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+		if (ce != cudaSuccess) return ce;
+		kernel<<<grid, block, smem, reinterpret_cast<cudaStream_t>(stream)>>>(tm_q, tm_kv, p);
+		return cudaSuccess;
+	};
+	cudaError_t ce;
+	if (d == 128) {
+		ce = go(x17::attn_fwd_kernel<128, DEBUG>, x17::attn_cfg::smem_bytes<128>());
+	} else if (d == 64) {
+		ce = go(x17::attn_fwd_kernel<64, DEBUG>, x17::attn_cfg::smem_bytes<64>());
+	} else {
+		ce = go(x17::attn_fwd_kernel<32, DEBUG>, x17::attn_cfg::smem_bytes<32>());
+	}
+	if (ce != cudaSuccess) {
+		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
+						 cudaGetErrorString(ce));
+	}
+	return launch_result(who);
+}
+
+// ---- GEMM --------------------------------------------------------------------------------------
+
+struct GemmPlan {
+	int epi;     // x17::GemmEpilogue
+	bool f8;     // kind::f8f6f4
+	bool split;  // e4m3 activations x split int8 weights: K doubled, A repeated
+};
+
+x17ai_DiagnosticBuffer *plan_gemm(x17ai_GemmConfig const *cfg, GemmPlan *plan, char const *who) {
+	if (cfg == nullptr) return make_diag("x17ai_b200: null config", who, ": null config");
+	bool const a_i8 = cfg->a_dtype == X17AI_DTYPE_INT8, a_f8 = cfg->a_dtype == X17AI_DTYPE_E4M3;
+	bool const b_i8 = cfg->b_dtype == X17AI_DTYPE_INT8, b_f8 = cfg->b_dtype == X17AI_DTYPE_E4M3;
+	if (!(a_i8 || a_f8) || !(b_i8 || b_f8) || (a_i8 && b_f8)) {
+		return make_diag("x17ai_b200: unsupported GEMM dtypes", who,
+						 ": gemm supports a/b dtypes int8/int8, e4m3/int8 and e4m3/e4m3");
+	}
+	plan->f8 = a_f8;
+	plan->split = a_f8 && b_i8;
+	if (cfg->a_cols == 0 || cfg->a_cols % 128 != 0) {
+		return make_diag("x17ai_b200: bad GEMM K", who, ": gemm requires a_cols to be a non-zero multiple of 128, got ",
+						 cfg->a_cols);
+	}
+	if (cfg->b_rows == 0 || cfg->b_rows % 128 != 0) {
+		return make_diag("x17ai_b200: bad GEMM N", who, ": gemm requires b_rows to be a non-zero multiple of 128, got ",
+						 cfg->b_rows);
+	}
+	switch (cfg->epilogue) {
+	case X17AI_EPILOGUE_SCALE:
+		if (cfg->c_dtype == X17AI_DTYPE_INT8) plan->epi = x17::EPI_SCALE_I8;
+		else if (cfg->c_dtype == X17AI_DTYPE_I32_RAW) plan->epi = x17::EPI_RAW_I32;
+		else return make_diag("x17ai_b200: bad GEMM output", who, ": scale epilogue writes int8 (or raw 32-bit)");
+		break;
+	case X17AI_EPILOGUE_RMS_NORM:
+		if (cfg->c_dtype != X17AI_DTYPE_INT8) {
+			return make_diag("x17ai_b200: bad GEMM output", who, ": rms-norm epilogue writes int8");
+		}
+		if (cfg->head_dim != 32 && cfg->head_dim != 64 && cfg->head_dim != 128) {
+			return make_diag("x17ai_b200: bad head_dim", who, ": rms-norm epilogue requires head_dim 32, 64 or 128, got ",
+							 cfg->head_dim);
+		}
+		if (cfg->b_rows % (2 * cfg->head_dim) != 0) {
+			return make_diag("x17ai_b200: bad GEMM N", who, ": rms-norm epilogue requires b_rows divisible by 2 * head_dim");
+		}
+		plan->epi = x17::EPI_L2NORM_KV;
+		break;
+	case X17AI_EPILOGUE_GEGLU:
+		if (cfg->c_dtype != X17AI_DTYPE_E4M3) {
+			return make_diag("x17ai_b200: bad GEMM output", who, ": geglu epilogue writes e4m3");
+		}
+		plan->epi = x17::EPI_GEGLU_E4M3;
+		break;
+	case X17AI_EPILOGUE_RESIDUAL:
+		if (cfg->c_dtype == X17AI_DTYPE_E4M3) plan->epi = x17::EPI_RESID_E4M3;
+		else if (cfg->c_dtype == X17AI_DTYPE_INT8) plan->epi = x17::EPI_RESID_I8;
+		else return make_diag("x17ai_b200: bad GEMM output", who, ": residual epilogue writes e4m3 or int8");
+		break;
+	default:
+		return make_diag("x17ai_b200: unknown epilogue", who, ": unknown epilogue ", cfg->epilogue);
+	}
+	return nullptr;
+}
+
+template <int EPI>
+cudaError_t gemm_go(bool f8, dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
+					x17::GemmParams const &p) {
+	uint32_t const smem = x17::gemm_cfg::SMEM_BYTES;
+	cudaError_t ce;
+	if (f8) {
+		ce = cudaFuncSetAttribute(x17::gemm_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+		if (ce != cudaSuccess) return ce;
+		x17::gemm_kernel<EPI, true><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb, p);
+	} else {
+		ce = cudaFuncSetAttribute(x17::gemm_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+		if (ce != cudaSuccess) return ce;
+		x17::gemm_kernel<EPI, false><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb, p);
+	}
+	return cudaSuccess;
+}
+
+__global__ void split_i8_weights_kernel(int8_t const *w, uint64_t rows, uint64_t cols, uint8_t *out) {
+	uint64_t const n = rows * cols;
+	for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
+		uint64_t const r = i / cols, c = i % cols;
+		int const v = w[i];
+		int const hi = (v + 128) / 16 - 8;  // floor(v / 16)
+		int const lo = v - 16 * hi;         // 0 .. 15
+		// standard e4m3 encodings of the integers 16*hi (multiples of 16 up to +-128) and lo
+		auto enc = [](int x) -> uint8_t {
+			if (x == 0) return 0;
+			uint32_t const s = x < 0 ? 0x80u : 0u;
+			uint32_t const a = uint32_t(x < 0 ? -x : x);
+			int const e = 31 - __clz(int(a));            // a = 1.mmm * 2^e, e <= 7
+			uint32_t const mant = e >= 3 ? (a >> (e - 3)) & 7u : (a << (3 - e)) & 7u;
+			return uint8_t(s | (uint32_t(e + 7) << 3) | mant);
+		};
+		out[r * 2 * cols + c] = enc(16 * hi);
+		out[r * 2 * cols + cols + c] = enc(lo);
+	}
+}
+
+
+
+// fixed-capacity FfiBuffer for x17ai_b200_take_diagnostic
+struct FixedBuf {
+	char *ptr;
+	size_t cap;
+	size_t len;
+};
+x17ai_FfiSpan fb_span(void *self) {
+	auto *b = static_cast<FixedBuf *>(self);
+	return x17ai_FfiSpan{b->ptr, b->len};
+}
+x17ai_FfiSpan fb_buf_span(void *self) {
+	auto *b = static_cast<FixedBuf *>(self);
+	return x17ai_FfiSpan{b->ptr, b->cap};
+}
+x17ai_FfiSpan fb_extend(void *self, size_t additional) {
+	auto *b = static_cast<FixedBuf *>(self);
+	size_t const room = b->cap - b->len;
+	size_t const n = additional <= room ? additional : 0;  // all or nothing, like Vec::try_reserve
+	x17ai_FfiSpan s{b->ptr + b->len, n};
+	b->len += n;
+	return s;
+}
+void fb_clear(void *self) { static_cast<FixedBuf *>(self)->len = 0; }
+void fb_set_len(void *self, size_t n) {
+	auto *b = static_cast<FixedBuf *>(self);
+	if (n <= b->cap) b->len = n;
+}
+x17ai_FfiBufferVMT const g_fixed_vmt{fb_span, fb_buf_span, fb_extend, fb_clear, fb_set_len};
+
+}  // namespace
+
+extern "C" {
+
+size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_t cap) {
+	if (diag == nullptr) return 0;
+	FixedBuf buf{dst, dst != nullptr ? cap : 0, 0};
+	x17ai_move_diagnostic(diag, x17ai_FfiBuffer{&buf, &g_fixed_vmt});
+	return buf.len;
+}
+
+uint64_t x17ai_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+x17ai_DiagnosticBuffer *x17ai_b200_read_status(x17ai_CudaStreamHandle *stream, uint32_t status[4]) {
+	char const *who = "x17ai_b200_read_status()";
+	if (status == nullptr) return static_diag("x17ai_b200_read_status(): null argument");
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+	cudaError_t e = cudaMemcpyAsync(status, scope.state().status, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+	if (e == cudaSuccess) e = cudaMemsetAsync(scope.state().status, 0, 4 * sizeof(uint32_t), s);
+	if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+	if (e != cudaSuccess) {
+		return make_diag("x17ai_b200_read_status(): failed", who, ": ", cudaGetErrorString(e));
+	}
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_meta(x17ai_AttnConfig const *cfg, x17ai_AttnMeta *meta) {
+	char const *who = "x17ai_b200_attn_meta()";
+	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (meta == nullptr) return static_diag("x17ai_b200_attn_meta(): null argument");
+	meta->threads_per_block = x17::attn_cfg::THREADS;
+	meta->q_per_block = x17::attn_cfg::BQ;
+	uint32_t smem = cfg->head_dim == 128 ? x17::attn_cfg::smem_bytes<128>()
+					: cfg->head_dim == 64 ? x17::attn_cfg::smem_bytes<64>()
+										  : x17::attn_cfg::smem_bytes<32>();
+	meta->smem_bytes = smem < 80u * 1024u ? 80u * 1024u : smem;
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size) {
+	return attn_launch<false>("x17ai_b200_attn_fwd_i8()", stream, cfg, batch, seq_len, q, kv, sink_k, sink_v,
+							  attn_temperature, out, l, window_size, nullptr, nullptr, nullptr);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_debug(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size,
+	int32_t *dbg_s, uint8_t *dbg_p, int32_t *dbg_o) {
+	if (!dbg_s || !dbg_p || !dbg_o) return static_diag("x17ai_b200_attn_fwd_i8_debug(): null debug buffer");
+	return attn_launch<true>("x17ai_b200_attn_fwd_i8_debug()", stream, cfg, batch, seq_len, q, kv, sink_k,
+							 sink_v, attn_temperature, out, l, window_size, dbg_s, dbg_p, dbg_o);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
+	int8_t const *q, int8_t const *kv_cache, size_t kv_capacity, size_t kv_len,
+	uint32_t const *kv_lens, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, size_t n_splits) {
+	char const *who = "x17ai_b200_attn_decode_i8()";
+	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (batch == 0) return make_diag("x17ai_b200: empty decode input", who, ": decode input q has zero size");
+	if (batch > 65535 || kv_capacity >= (size_t(1) << 31) || kv_len > kv_capacity) {
+		return make_diag("x17ai_b200: decode shape out of range", who, ": decode shape out of range (kv_len ",
+						 kv_len, ", kv_capacity ", kv_capacity, ")");
+	}
+	if (window_size > 0 && window_size % 16 != 0) {
+		return make_diag("x17ai_b200: bad window", who,
+						 ": attention window_size must be zero or divisible by 16, got ", window_size);
+	}
+	if (!q || !kv_cache || !sink_k || !sink_v || !attn_temperature || !out) {
+		return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	}
+	if (!aligned16(q) || !aligned16(kv_cache) || !aligned16(sink_k)) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+
+	size_t const pairs = batch * cfg->n_heads;
+	if (n_splits == 0) {  // choose: enough CTAs for two waves of 4 CTAs per SM
+		size_t const want = size_t(scope.state().sm_count) * 8;
+		n_splits = pairs >= want ? 1 : (want + pairs - 1) / pairs;
+		size_t const max_splits = kv_len / 256 > 0 ? kv_len / 256 : 1;
+		if (n_splits > max_splits) n_splits = max_splits;
+	}
+	if (n_splits > 65535) n_splits = 65535;
+
+	uint32_t const d = uint32_t(cfg->head_dim);
+	x17::DecodeParams p{};
+	p.q = q;
+	p.q_stride = cfg->q_stride;
+	p.kv = kv_cache;
+	p.kv_stride = cfg->kv_stride;
+	p.kv_batch_stride = cfg->kv_stride * kv_capacity;
+	p.kv_lens = kv_lens;
+	p.kv_len = uint32_t(kv_len);
+	p.window = window_size == 0 ? 0xFFFFFFFFu : uint32_t(((window_size - 1) / 16 + 1) * 16);
+	p.sink_k = sink_k;
+	p.sink_v = sink_v;
+	p.temperature = attn_temperature;
+	p.out = out;
+	p.o_stride = cfg->o_stride;
+	p.l = l;
+	p.n_heads = uint32_t(cfg->n_heads);
+	p.n_splits = uint32_t(n_splits);
+	p.scratch = nullptr;
+	if (n_splits > 1) {
+		size_t const bytes = pairs * n_splits * (d + 2) * sizeof(float);
+		cudaError_t e = cudaMallocAsync(reinterpret_cast<void **>(&p.scratch), bytes, s);
+		if (e != cudaSuccess) {
+			return make_diag("x17ai_b200: scratch allocation failed", who, ": cudaMallocAsync(", bytes,
+							 ") failed: ", cudaGetErrorString(e));
+		}
+	}
+	dim3 grid(unsigned(cfg->n_heads), unsigned(batch), unsigned(n_splits));
+	dim3 mgrid(unsigned(cfg->n_heads), unsigned(batch));
+	if (d == 128) {
+		x17::attn_decode_kernel<128><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>(p);
+	} else if (d == 64) {
+		x17::attn_decode_kernel<64><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>(p);
+	} else {
+		x17::attn_decode_kernel<32><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<32><<<mgrid, 32, 0, s>>>(p);
+	}
+	x17ai_DiagnosticBuffer *res = launch_result(who);
+	if (n_splits > 1) {
+		if (res == nullptr) g_launches.fetch_add(1, std::memory_order_relaxed);
+		cudaFreeAsync(p.scratch, s);
+	}
+	return res;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_meta(x17ai_GemmConfig const *cfg, x17ai_GemmMeta *meta) {
+	GemmPlan plan{};
+	if (auto *d = plan_gemm(cfg, &plan, "x17ai_b200_gemm_meta()")) return d;
+	if (meta == nullptr) return static_diag("x17ai_b200_gemm_meta(): null argument");
+	meta->threads_per_block = x17::gemm_cfg::THREADS;
+	meta->smem_bytes = x17::gemm_cfg::SMEM_BYTES;
+	meta->m_per_block = x17::gemm_cfg::BM;
+	meta->n_per_block = x17::gemm_cfg::BN;
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
+	x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
+	void const *a, size_t a_rows, void const *b, size_t b_rows,
+	void *c, float *rrms, int8_t const *residual) {
+	char const *who = "x17ai_b200_gemm_fwd()";
+	GemmPlan plan{};
+	if (auto *d = plan_gemm(cfg, &plan, who)) return d;
+	if (a_rows == 0) return make_diag("x17ai_b200: empty GEMM input", who, ": gemm input a has zero size");
+	if (b_rows != cfg->b_rows) {
+		return make_diag("x17ai_b200: bad GEMM shape", who, ": gemm input b has ", b_rows,
+						 " rows, but should have ", cfg->b_rows);
+	}
+	if (a_rows >= (size_t(1) << 31) || cfg->b_rows >= (size_t(1) << 31) || cfg->a_cols >= (size_t(1) << 30)) {
+		return make_diag("x17ai_b200: GEMM shape out of range", who, ": gemm shape out of range");
+	}
+	if (!a || !b || !c) return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	if (plan.epi == x17::EPI_L2NORM_KV && rrms == nullptr) {
+		return make_diag("x17ai_b200: null tensor", who, ": rms-norm epilogue needs the rrms output");
+	}
+	if ((plan.epi == x17::EPI_RESID_E4M3 || plan.epi == x17::EPI_RESID_I8) && residual == nullptr) {
+		return make_diag("x17ai_b200: null tensor", who, ": residual epilogue needs the residual input");
+	}
+	if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (residual && !aligned16(residual))) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+
+	using namespace x17::gemm_cfg;
+	size_t const k_a = cfg->a_cols;
+	size_t const k_total = plan.split ? 2 * k_a : k_a;
+	CUtensorMap ta, tb;
+	CUresult e = make_map_2d(&ta, a, k_a, a_rows, k_a, BK, BM);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, b, k_total, cfg->b_rows, k_total, BK, BN);
+	if (e != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
+						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
+	}
+	x17::GemmParams p{};
+	p.m = uint32_t(a_rows);
+	p.n_raw = uint32_t(cfg->b_rows);
+	p.k = uint32_t(k_total);
+	p.k_a = uint32_t(k_a);
+	p.tiles_m = uint32_t((a_rows + BM - 1) / BM);
+	p.tiles_n = uint32_t((cfg->b_rows + BN - 1) / BN);
+	p.c = c;
+	p.residual = residual;
+	p.rrms = rrms;
+	p.head_dim = uint32_t(cfg->head_dim);
+	p.status = scope.state().status;
+	double const inp = cfg->inp_scale, out = cfg->out_scale;
+	switch (plan.epi) {
+	case x17::EPI_SCALE_I8:
+	case x17::EPI_RAW_I32:
+		p.c_stride = cfg->b_rows;
+		p.k0 = float(inp * out);
+		break;
+	case x17::EPI_L2NORM_KV:
+		p.c_stride = cfg->b_rows;
+		p.rrms_cols = uint32_t(cfg->b_rows / (2 * cfg->head_dim));
+		p.k0 = float(cfg->eps);
+		p.k1 = float(out * std::sqrt(double(cfg->head_dim)));  // gemm.rs:146
+		p.k2 = float(inp * out);                               // gemm.rs:152
+		break;
+	case x17::EPI_GEGLU_E4M3: {
+		// math::fast::gelu<INP^2, INP^2 * OUT^2, 1> (cuda/utils_core.cuh:426-448)
+		p.c_stride = cfg->b_rows / 2;
+		double const inp2 = inp * inp;
+		double const ck = std::sqrt(inp2 * 2.0 / M_PI);
+		p.k0 = float(0.044715 * ck * inp2);
+		p.k1 = float(ck);
+		p.k2 = float(0.5 * std::sqrt(inp2 * out * out) * std::sqrt(inp2));
+		break;
+	}
+	default:  // residual (cuda/gemm_b8.cuh:484-505, cuda/utils_core.cuh:397-405,468-483)
+		p.c_stride = cfg->b_rows / 2;
+		p.resid_stride = cfg->b_rows / 2;
+		p.k0 = float(0.5 * (1.0 / 8.0));
+		p.k1 = float(M_LN2 * -inp);
+		p.k2 = float(inp * 2.0);
+		p.k3 = float(inp * out / 2.0);
+		p.k4 = float(inp * inp * out);
+		break;
+	}
+	uint32_t const n_tiles = p.tiles_m * p.tiles_n;
+	uint32_t const ctas = n_tiles < uint32_t(scope.state().sm_count) ? n_tiles : uint32_t(scope.state().sm_count);
+	dim3 grid(ctas);
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+	cudaError_t ce;
+	switch (plan.epi) {
+	case x17::EPI_SCALE_I8: ce = gemm_go<x17::EPI_SCALE_I8>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_RAW_I32: ce = gemm_go<x17::EPI_RAW_I32>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_L2NORM_KV: ce = gemm_go<x17::EPI_L2NORM_KV>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_GEGLU_E4M3: ce = gemm_go<x17::EPI_GEGLU_E4M3>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_RESID_E4M3: ce = gemm_go<x17::EPI_RESID_E4M3>(plan.f8, grid, s, ta, tb, p); break;
+	default: ce = gemm_go<x17::EPI_RESID_I8>(plan.f8, grid, s, ta, tb, p); break;
+	}
+	if (ce != cudaSuccess) {
+		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
+						 cudaGetErrorString(ce));
+	}
+	return launch_result(who);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_split_i8_weights(
+	x17ai_CudaStreamHandle *stream, int8_t const *w, size_t rows, size_t cols, uint8_t *out) {
+	char const *who = "x17ai_b200_split_i8_weights()";
+	if (!w || !out || rows == 0 || cols == 0) return make_diag("x17ai_b200: bad argument", who, ": bad argument");
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	split_i8_weights_kernel<<<scope.state().sm_count * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+		w, rows, cols, out);
+	return launch_result(who);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_rms_norm(
+	x17ai_CudaStreamHandle *stream, int32_t mode, void const *inp, size_t rows, size_t cols,
+	int8_t *out, float *row_scale, double eps) {
+	char const *who = "x17ai_b200_rms_norm()";
+	if (mode < 0 || mode > 2) return make_diag("x17ai_b200: bad mode", who, ": unknown mode ", mode);
+	if (rows == 0 || cols == 0) return make_diag("x17ai_b200: empty input", who, ": rms_norm input has zero size");
+	size_t const vals = mode == X17AI_RMS_E4M3_FIXED ? 16 : 8;
+	if (cols % 16 != 0 || cols / vals > size_t(x17::rms_cfg::MAX_CHUNKS) * 32) {
+		return make_diag("x17ai_b200: bad rms_norm width", who, ": rms_norm requires cols to be a multiple of 16 and at most ",
+						 vals * x17::rms_cfg::MAX_CHUNKS * 32, ", got ", cols);
+	}
+	if (rows >= (size_t(1) << 31)) return make_diag("x17ai_b200: rms_norm shape out of range", who, ": too many rows");
+	if (!inp || !out || (mode == X17AI_RMS_BF16_ROWSCALE && !row_scale)) {
+		return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	}
+	if (!aligned16(inp) || !aligned16(out)) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	x17::RmsParams p{};
+	p.inp = inp;
+	p.out = out;
+	p.row_scale = row_scale;
+	p.rows = uint32_t(rows);
+	p.cols = uint32_t(cols);
+	p.inp_stride = cols;
+	p.out_stride = cols;
+	p.eps = float(eps);
+	p.inv_cols = float(1.0 / double(cols));
+	dim3 grid(unsigned((rows + x17::rms_cfg::WARPS - 1) / x17::rms_cfg::WARPS));
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+	if (mode == X17AI_RMS_E4M3_FIXED) {
+		x17::rms_norm_kernel<x17::RMS_E4M3_FIXED><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+	} else if (mode == X17AI_RMS_BF16_FIXED) {
+		x17::rms_norm_kernel<x17::RMS_BF16_FIXED><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+	} else {
+		x17::rms_norm_kernel<x17::RMS_BF16_ROWSCALE><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+	}
+	return launch_result(who);
+}
+
+}  // extern "C"

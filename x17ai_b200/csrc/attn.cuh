@@ -1,0 +1,431 @@
+// int8 sliding-window attention forward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// Replaces AttnForward<...>::run (cuda/attn_fwd_i8.cuh:368-619) behind the same argument list
+// (templates/attn/kernel.cu:9-20), with a batch dimension added as grid.z.
+//
+// Semantics kept from the reference: a query i attends keys i-W' .. i-1 (W' = window rounded up
+// to 16, 0 = unbounded) plus a per-head sink token; scores are exact int32 dot products times
+// the temperature D^-1/2 / 64 * log2(min(W', i) + 4) * temp_h; probabilities are quantised to
+// u8 steps of 1/255 and multiplied with V on the int8 tensor cores; the normaliser uses the
+// un-rounded probabilities; out = rint(clamp(O / sum)) as FixedI8 and L = log2(sum) + max.
+//
+// What differs from the reference's schedule: the row maximum is found first (a first sweep of
+// Q.K^T over the visible KV tiles that only reduces max), then a second sweep quantises P
+// against that final maximum.  P.V therefore accumulates exactly in int32 in TMEM across all
+// KV tiles with no rescaling, and the result does not depend on the KV tile size.
+//
+// One CTA = 128 queries of one (batch, head); two CTAs per SM. 192 threads:
+//   warp 0      TMA producer (Q once; K tiles for sweep 1; K and V tiles for sweep 2)
+//   warp 1      MMA issuer: S = Q.K^T (kind::i8, M128 N128 K32 x D/32) into TMEM columns [0,128),
+//               O += P.V (u8 x s8, V read MN-major straight from its [key][dim] tile) into
+//               TMEM columns [128, 128+D)
+//   warps 2..5  one thread per query row: tcgen05.ld of its S row, max / exp2 / quantise,
+//               P written to shared memory in the 128B-swizzled K-major layout, final
+//               normalisation and 16-byte stores
+// KV tiles wholly outside [i-W', i-1] for every row of the CTA are never loaded.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace x17 {
+
+struct AttnParams {
+	u32 seq_len;
+	u32 n_heads;
+	u32 window;  // already rounded up to 16; 0xFFFFFFFF = unbounded
+	i8 const *q;
+	u64 q_stride, q_batch_stride;
+	i8 const *sink_k;
+	i8 const *sink_v;
+	f32 const *temperature;
+	i8 *out;
+	u64 o_stride, o_batch_stride;
+	f32 *l;  // [batch][head][seq] or null
+	u64 l_batch_stride;
+	u32 *status;
+	// validation outputs (only read by the DEBUG instantiation), dense per (batch, head):
+	i32 *dbg_s;  // [seq][seq] raw scores of every visited tile
+	u8 *dbg_p;   // [seq][seq] quantised probabilities
+	i32 *dbg_o;  // [seq][D] int32 P.V accumulator
+};
+
+namespace attn_cfg {
+constexpr u32 BQ = 128;   // queries per CTA
+constexpr u32 BKV = 128;  // keys per tile
+constexpr u32 STAGES = 4;
+constexpr u32 THREADS = 192;
+constexpr u32 TMEM_COLS = 256;
+constexpr u32 O_COL = 128;
+template <u32 D>
+constexpr u32 smem_bytes() {
+	return BQ * D + STAGES * BKV * D + BQ * BKV + 1024 + 256;
+}
+constexpr f32 MAGIC = 12582912.0f;  // 1.5 * 2^23
+constexpr u32 MAGIC_BITS = 0x4B400000u;
+}  // namespace attn_cfg
+
+X17_DEV void st_shared_v4(u32 addr, u32 a, u32 b, u32 c, u32 d) {
+	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+				 : "memory");
+}
+
+template <u32 D, bool DEBUG>
+__global__ void __launch_bounds__(attn_cfg::THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+				const AttnParams p) {
+	using namespace attn_cfg;
+	static_assert(D == 32 || D == 64 || D == 128, "head_dim must be 32, 64 or 128");
+	constexpr u32 TILE_BYTES = BKV * D;
+
+	extern __shared__ u8 smem_raw[];
+	u32 const smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	u8 *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+	u32 const s_q = smem_base;
+	u32 const s_ring = s_q + BQ * D;
+	u32 const s_p = s_ring + STAGES * TILE_BYTES;
+	u32 const bar_base = s_p + BQ * BKV;
+	auto full_bar = [&](u32 s) { return bar_base + 8 * s; };
+	auto empty_bar = [&](u32 s) { return bar_base + 8 * (STAGES + s); };
+	u32 const q_full_bar = bar_base + 8 * (2 * STAGES + 0);
+	u32 const s_full_bar = bar_base + 8 * (2 * STAGES + 1);
+	u32 const s_done_bar = bar_base + 8 * (2 * STAGES + 2);
+	u32 const o_full_bar = bar_base + 8 * (2 * STAGES + 3);
+	u32 const tmem_slot = bar_base + 8 * (2 * STAGES + 4);
+	volatile u32 *const tmem_slot_gen = reinterpret_cast<volatile u32 *>(
+		smem_gen + (BQ * D + STAGES * TILE_BYTES + BQ * BKV) + 8 * (2 * STAGES + 4));
+	volatile u32 *const abort_flag = tmem_slot_gen + 1;
+	WaitCtx const ctx{abort_flag, p.status};
+
+	u32 const warp = threadIdx.x >> 5;
+	u32 const lane = threadIdx.x & 31;
+
+	// heavier query tiles (more visible keys) first
+	u32 const q_tile = gridDim.x - 1 - blockIdx.x;
+	u32 const head = blockIdx.y;
+	u32 const batch = blockIdx.z;
+	u32 const q0 = q_tile * BQ;
+	u32 const w = p.window;
+
+	// visible KV tiles: keys max(0, q0 - W') .. q0 + BQ - 2  (the last row sees up to q0+BQ-2)
+	u32 const t_begin = (w == 0xFFFFFFFFu || q0 < w) ? 0u : (q0 - w) / BKV;
+	u32 const t_end = q_tile;  // inclusive; BQ == BKV, so the diagonal tile has the CTA's index
+	u32 const n_tiles = t_end - t_begin + 1;
+
+	if (threadIdx.x == 0) {
+		for (u32 s = 0; s < STAGES; ++s) {
+			mbar_init(full_bar(s), 1);
+			mbar_init(empty_bar(s), 1);
+		}
+		mbar_init(q_full_bar, 1);
+		mbar_init(s_full_bar, 1);
+		mbar_init(s_done_bar, 128);
+		mbar_init(o_full_bar, 1);
+		*abort_flag = 0;
+		mbar_fence_init();
+	}
+	if (warp == 1) {
+		tmem_alloc(tmem_slot, TMEM_COLS);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	u32 const tmem_base = *tmem_slot_gen;
+
+	if (warp == 0) {
+		// ---------------- TMA producer ----------------
+		if (elect_one()) {
+			tma_prefetch_desc(&tm_q);
+			tma_prefetch_desc(&tm_kv);
+			mbar_expect_tx(q_full_bar, BQ * D);
+			tma_load_3d(s_q, &tm_q, q_full_bar, i32(head * D), i32(q0), i32(batch));
+			u32 it = 0;
+			bool ok = true;
+			for (u32 sweep = 0; sweep < 2 && ok; ++sweep) {
+				for (u32 t = t_begin; t <= t_end && ok; ++t) {
+					u32 const n_items = sweep == 0 ? 1u : 2u;  // K only, then K and V
+					for (u32 item = 0; item < n_items; ++item, ++it) {
+						u32 const s = it % STAGES;
+						u32 const ph = (it / STAGES) & 1;
+						if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, ST_WAIT_STAGE_EMPTY, s)) {
+							ok = false;
+							break;
+						}
+						mbar_expect_tx(full_bar(s), TILE_BYTES);
+						tma_load_3d(s_ring + s * TILE_BYTES, &tm_kv, full_bar(s),
+									i32(2 * head * D + item * D), i32(t * BKV), i32(batch));
+					}
+				}
+			}
+		}
+	} else if (warp == 1) {
+		// ---------------- MMA issuer ----------------
+		if (elect_one()) {
+			constexpr u32 idesc_qk = make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, BQ, BKV);
+			constexpr u32 idesc_pv = make_idesc(DFMT_S32, FMT_U8, FMT_S8, 0, 1, BQ, D);
+			u32 const s_tmem = tmem_base;
+			u32 const o_tmem = tmem_base + O_COL;
+			bool ok = mbar_wait(q_full_bar, 0, ctx, ST_WAIT_Q_FULL, 0);
+			u32 it = 0;
+			u32 s_it = 0;
+			for (u32 sweep = 0; sweep < 2 && ok; ++sweep) {
+				for (u32 t = t_begin; t <= t_end && ok; ++t) {
+					{  // S = Q . K^T
+						u32 const s = it % STAGES;
+						u32 const ph = (it / STAGES) & 1;
+						if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
+							ok = false;
+							break;
+						}
+						tc_fence_after();
+						u64 const adesc = make_smem_desc(s_q, D);
+						u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+#pragma unroll
+						for (u32 ks = 0; ks < D / 32; ++ks) {
+							mma_i8_ss(s_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
+						}
+						tc_commit(empty_bar(s));
+						tc_commit(s_full_bar);
+						++it;
+					}
+					// rows have read S (sweep 1) / written P (sweep 2)
+					if (!mbar_wait(s_done_bar, s_it & 1, ctx, ST_WAIT_S_DONE, t)) {
+						ok = false;
+						break;
+					}
+					++s_it;
+					tc_fence_after();
+					if (sweep == 1) {  // O += P . V
+						u32 const s = it % STAGES;
+						u32 const ph = (it / STAGES) & 1;
+						if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
+							ok = false;
+							break;
+						}
+						tc_fence_after();
+						u64 const adesc = make_smem_desc(s_p, 128);
+						u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+#pragma unroll
+						for (u32 ks = 0; ks < BKV / 32; ++ks) {
+							// A: +32 bytes along the key axis inside the swizzle row;
+							// B (MN-major): +32 key rows of D bytes each
+							mma_i8_ss(o_tmem, adesc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
+									  (t != t_begin || ks != 0) ? 1u : 0u);
+						}
+						tc_commit(empty_bar(s));
+						++it;
+					}
+				}
+			}
+			if (ok) tc_commit(o_full_bar);
+		}
+	} else {
+		// ---------------- one thread per query row ----------------
+		u32 const quarter = warp & 3;
+		u32 const row = quarter * 32 + lane;
+		u32 const qi = q0 + row;
+		bool const row_ok = qi < p.seq_len;
+		u32 const lane_addr = (quarter * 32u) << 16;
+
+		// sink score: exact int32 dot product of this row's q with sink_k
+		i32 sink_dot = 0;
+		if (row_ok) {
+			uint4 const *qrow = reinterpret_cast<uint4 const *>(
+				p.q + u64(batch) * p.q_batch_stride + u64(qi) * p.q_stride + head * D);
+			uint4 const *sk = reinterpret_cast<uint4 const *>(p.sink_k + head * D);
+#pragma unroll
+			for (u32 i = 0; i < D / 16; ++i) {
+				uint4 a = qrow[i];
+				uint4 b = __ldg(sk + i);
+				sink_dot = __dp4a(i32(a.x), i32(b.x), sink_dot);
+				sink_dot = __dp4a(i32(a.y), i32(b.y), sink_dot);
+				sink_dot = __dp4a(i32(a.z), i32(b.z), sink_dot);
+				sink_dot = __dp4a(i32(a.w), i32(b.w), sink_dot);
+			}
+		}
+		// temperature (attn_fwd_i8.cuh:444-450, :497)
+		u32 const n_att = (qi < w ? qi : w) + 4u;
+		f32 const base_t = f32((1.0 / 64.0) * (D == 128 ? 0.08838834764831845 : D == 64 ? 0.125 : 0.17677669529663687));
+		f32 const row_t = __fmul_rn(base_t, lg2_approx(f32(n_att)));
+		f32 const temp = __fmul_rn(row_t, __ldg(p.temperature + head));
+		f32 const sink_s = __fmul_rn(__int2float_rn(sink_dot), temp);
+
+		u32 s_it = 0;
+		bool ok = true;
+
+		// ---- sweep 1: row maximum over the visible keys ----
+		i32 acc_max = INT32_MIN;
+		i32 acc_min = INT32_MAX;
+		for (u32 t = t_begin; t <= t_end && ok; ++t) {
+			if (!mbar_wait_warp(s_full_bar, s_it & 1, ctx, ST_WAIT_S_FULL, t)) {
+				ok = false;
+				break;
+			}
+			++s_it;
+			tc_fence_after();
+			u32 const k0 = t * BKV;
+			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
+			for (u32 c = 0; c < BKV; c += 32) {
+				u32 r[32];
+				tmem_ld_32x32b_x32(tmem_base + lane_addr + c, r);
+				tmem_wait_ld();
+				if (edge) {
+#pragma unroll
+					for (u32 i = 0; i < 32; ++i) {
+						u32 const j = k0 + c + i;
+						bool const valid = j < qi && (w == 0xFFFFFFFFu || j + w >= qi);
+						if (valid) {
+							acc_max = max(acc_max, i32(r[i]));
+							acc_min = min(acc_min, i32(r[i]));
+						}
+					}
+				} else {
+#pragma unroll
+					for (u32 i = 0; i < 32; ++i) {
+						acc_max = max(acc_max, i32(r[i]));
+						acc_min = min(acc_min, i32(r[i]));
+					}
+				}
+				if constexpr (DEBUG) {
+					if (row_ok) {
+						i32 *dst = p.dbg_s + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
+								   + u64(qi) * p.seq_len + k0 + c;
+#pragma unroll
+						for (u32 i = 0; i < 32; ++i) {
+							if (k0 + c + i < p.seq_len) dst[i] = i32(r[i]);
+						}
+					}
+				}
+			}
+			tc_fence_before();
+			mbar_arrive(s_done_bar);
+		}
+		f32 m = sink_s;
+		if (acc_max >= acc_min) {  // at least one visible key
+			f32 const cand = temp >= 0.0f ? __fmul_rn(__int2float_rn(acc_max), temp)
+										  : __fmul_rn(__int2float_rn(acc_min), temp);
+			m = fmaxf(m, cand);
+		}
+
+		// ---- sweep 2: probabilities against the final maximum ----
+		f32 const neg_m = -m;
+		f32 sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+		u32 const p_row = s_p + row * 128u;
+		u32 const sw = row & 7u;
+		for (u32 t = t_begin; t <= t_end && ok; ++t) {
+			if (!mbar_wait_warp(s_full_bar, s_it & 1, ctx, ST_WAIT_S_FULL, t)) {
+				ok = false;
+				break;
+			}
+			++s_it;
+			tc_fence_after();
+			u32 const k0 = t * BKV;
+			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
+			for (u32 c = 0; c < BKV; c += 32) {
+				u32 r[32];
+				tmem_ld_32x32b_x32(tmem_base + lane_addr + c, r);
+				tmem_wait_ld();
+				u32 pk[8];
+#pragma unroll
+				for (u32 g = 0; g < 8; ++g) {
+					u32 q4[4];
+#pragma unroll
+					for (u32 e = 0; e < 4; ++e) {
+						u32 const i = 4 * g + e;
+						// exact int -> float without the conversion unit (|acc| < 2^22)
+						f32 const f = __fsub_rn(__uint_as_float(r[i] + MAGIC_BITS), MAGIC);
+						f32 x = __fmaf_rn(f, temp, neg_m);
+						if (edge) {
+							u32 const j = k0 + c + i;
+							bool const valid = j < qi && (w == 0xFFFFFFFFu || j + w >= qi);
+							x = valid ? x : -INFINITY;
+						}
+						f32 const ex = ex2_approx(x);
+						if (e == 0) sum0 = __fadd_rn(sum0, ex);
+						if (e == 1) sum1 = __fadd_rn(sum1, ex);
+						if (e == 2) sum2 = __fadd_rn(sum2, ex);
+						if (e == 3) sum3 = __fadd_rn(sum3, ex);
+						// rint(255 * ex) lands in the low mantissa byte
+						q4[e] = __float_as_uint(__fmaf_rn(ex, 255.0f, MAGIC));
+					}
+					u32 const lo = __byte_perm(q4[0], q4[1], 0x0040);
+					u32 const hi = __byte_perm(q4[2], q4[3], 0x0040);
+					pk[g] = __byte_perm(lo, hi, 0x5410);
+				}
+				u32 const ch = c >> 4;  // first of the two 16-byte chunks of this row
+				st_shared_v4(p_row + (((ch + 0) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+				st_shared_v4(p_row + (((ch + 1) ^ sw) << 4), pk[4], pk[5], pk[6], pk[7]);
+				if constexpr (DEBUG) {
+					if (row_ok) {
+						u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
+								  + u64(qi) * p.seq_len + k0 + c;
+#pragma unroll
+						for (u32 i = 0; i < 32; ++i) {
+							if (k0 + c + i < p.seq_len) dst[i] = u8(pk[i >> 2] >> (8 * (i & 3)));
+						}
+					}
+				}
+			}
+			fence_proxy_async_smem();
+			tc_fence_before();
+			mbar_arrive(s_done_bar);
+		}
+
+		// ---- normalise and store ----
+		if (ok && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
+			tc_fence_after();
+			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
+			f32 const sum = __fmul_rn(
+				__fadd_rn(__fadd_rn(__fadd_rn(sum0, sum1), __fadd_rn(sum2, sum3)), sink_e), 255.0f);
+			f32 const w_sink = __fmul_rn(sink_e, 255.0f);
+			f32 const recip = rcp_approx(sum);
+			i8 *const out_row =
+				p.out + u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D;
+			for (u32 c = 0; c < D; c += 32) {
+				u32 r[32];
+				tmem_ld_32x32b_x32(tmem_base + lane_addr + O_COL + c, r);
+				tmem_wait_ld();
+				uint4 const sv0 = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + c));
+				uint4 const sv1 = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + c) + 1);
+				u32 const svw[8] = {sv0.x, sv0.y, sv0.z, sv0.w, sv1.x, sv1.y, sv1.z, sv1.w};
+				u32 pk[8];
+#pragma unroll
+				for (u32 g = 0; g < 8; ++g) {
+					u32 b4[4];
+#pragma unroll
+					for (u32 e = 0; e < 4; ++e) {
+						f32 const sv = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
+						f32 const o = __fmaf_rn(w_sink, sv, __int2float_rn(i32(r[4 * g + e])));
+						b4[e] = u32(f32_to_fixedi8(__fmul_rn(o, recip)));
+					}
+					pk[g] = pack4(b4[0], b4[1], b4[2], b4[3]);
+				}
+				if (row_ok) {
+					uint4 *dst = reinterpret_cast<uint4 *>(out_row + c);
+					dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+					dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+					if constexpr (DEBUG) {
+						i32 *d = p.dbg_o + ((u64(batch) * p.n_heads + head) * p.seq_len + qi) * D + c;
+#pragma unroll
+						for (u32 i = 0; i < 32; ++i) d[i] = i32(r[i]);
+					}
+				}
+			}
+			if (row_ok && p.l != nullptr) {
+				p.l[u64(batch) * p.l_batch_stride + u64(head) * p.seq_len + qi] =
+					__fadd_rn(lg2_approx(sum), m);
+			}
+		}
+	}
+
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 1) {
+		__syncwarp();
+		tc_fence_after();
+		tmem_dealloc(tmem_base, TMEM_COLS);
+	}
+}
+
+}  // namespace x17

@@ -1,0 +1,148 @@
+// Row-wise RMSNorm -> FixedI8, HBM-bound (no tensor cores).
+//
+// Replaces Rms_norm::kernel (rms_norm.cu:55-113): y = fixedi8(x * rsqrt(mean(x^2) + eps) * 8)
+// with x decoded from the reference's e4m3 (cuda/utils_b8.cuh:652-657).  The sum of squares
+// is taken in the reference's order (16 consecutive values per lane and 512-value step as an
+// fma chain from zero, added to the lane's running sum, then a butterfly over the warp), so
+// the result matches the reference kernel bit for bit.
+//
+// One warp per row, 16-byte loads and stores; the row stays in registers between the two
+// passes (up to 8192 columns), so every input byte is read from HBM once.
+// Two additional input/output modes: bf16 input, and int8 output with a per-row
+// absmax/127 scale instead of the fixed scale 8.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace x17 {
+
+enum RmsMode : int {
+	RMS_E4M3_FIXED = 0,   // e4m3 in, FixedI8 out (reference form)
+	RMS_BF16_FIXED = 1,   // bf16 in, FixedI8 out
+	RMS_BF16_ROWSCALE = 2 // bf16 in, int8 out + f32 per-row scale (absmax / 127)
+};
+
+struct RmsParams {
+	void const *inp;
+	i8 *out;
+	f32 *row_scale;  // RMS_BF16_ROWSCALE only
+	u32 rows, cols;
+	u64 inp_stride, out_stride;  // elements
+	f32 eps, inv_cols;
+};
+
+namespace rms_cfg {
+constexpr u32 WARPS = 8;
+constexpr u32 THREADS = WARPS * 32;
+constexpr u32 MAX_CHUNKS = 16;  // 16-byte chunks per lane held in registers
+}  // namespace rms_cfg
+
+X17_DEV f32 bf16_lo(u32 w) { return __uint_as_float(w << 16); }
+X17_DEV f32 bf16_hi(u32 w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+template <int MODE>
+__global__ void __launch_bounds__(rms_cfg::THREADS)
+rms_norm_kernel(const RmsParams p) {
+	using namespace rms_cfg;
+	constexpr u32 VALS = MODE == RMS_E4M3_FIXED ? 16 : 8;  // values per 16-byte chunk
+	u32 const warp = threadIdx.x >> 5;
+	u32 const lane = threadIdx.x & 31;
+	u32 const row = blockIdx.x * WARPS + warp;
+	if (row >= p.rows) return;
+
+	u32 const n_chunks = p.cols / VALS;           // 16-byte chunks per row
+	u32 const per_lane = (n_chunks + 31) / 32;    // <= MAX_CHUNKS (checked on the host)
+	uint4 const *src = reinterpret_cast<uint4 const *>(
+		static_cast<u8 const *>(p.inp) + u64(row) * p.inp_stride * (MODE == RMS_E4M3_FIXED ? 1 : 2));
+
+	uint4 regs[MAX_CHUNKS];
+	f32 local = 0.0f;
+	f32 amax = 0.0f;
+#pragma unroll
+	for (u32 s = 0; s < MAX_CHUNKS; ++s) {
+		if (s < per_lane) {
+			u32 const ci = s * 32 + lane;
+			uint4 v = make_uint4(0, 0, 0, 0);
+			if (ci < n_chunks) v = __ldg(src + ci);
+			regs[s] = v;
+			u32 const wds[4] = {v.x, v.y, v.z, v.w};
+			f32 acc = 0.0f;
+#pragma unroll
+			for (u32 i = 0; i < 4; ++i) {
+				if constexpr (MODE == RMS_E4M3_FIXED) {
+#pragma unroll
+					for (u32 j = 0; j < 4; ++j) {
+						f32 x = e4m3_to_f32((wds[i] >> (8 * j)) & 0xFFu);
+						acc = __fmaf_rn(x, x, acc);
+					}
+				} else {
+					f32 x0 = bf16_lo(wds[i]), x1 = bf16_hi(wds[i]);
+					acc = __fmaf_rn(x0, x0, acc);
+					acc = __fmaf_rn(x1, x1, acc);
+					amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+				}
+			}
+			local = __fadd_rn(local, acc);
+		}
+	}
+#pragma unroll
+	for (u32 mask = 16; mask > 0; mask >>= 1) {
+		local = __fadd_rn(local, __shfl_xor_sync(0xffffffffu, local, mask));
+		if constexpr (MODE == RMS_BF16_ROWSCALE) {
+			amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
+		}
+	}
+	f32 const rrms = rsqrt_approx(__fmaf_rn(local, p.inv_cols, p.eps));
+	f32 mul = rrms;
+	if constexpr (MODE == RMS_BF16_ROWSCALE) {
+		// scale = absmax(x * rrms) / 127; codes = rint(x * rrms / scale)
+		f32 const scale = __fmul_rn(__fmul_rn(amax, rrms), 1.0f / 127.0f);
+		if (lane == 0) p.row_scale[row] = scale;
+		mul = scale > 0.0f ? __fdiv_rn(rrms, scale) : 0.0f;
+	}
+
+	if constexpr (MODE == RMS_E4M3_FIXED) {
+		uint4 *dst = reinterpret_cast<uint4 *>(p.out + u64(row) * p.out_stride);
+#pragma unroll
+		for (u32 s = 0; s < MAX_CHUNKS; ++s) {
+			if (s < per_lane) {
+				u32 const ci = s * 32 + lane;
+				u32 const wds[4] = {regs[s].x, regs[s].y, regs[s].z, regs[s].w};
+				u32 o[4];
+#pragma unroll
+				for (u32 i = 0; i < 4; ++i) {
+					u32 b[4];
+#pragma unroll
+					for (u32 j = 0; j < 4; ++j) {
+						f32 x = e4m3_to_f32((wds[i] >> (8 * j)) & 0xFFu);
+						b[j] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(x, mul), 8.0f)));
+					}
+					o[i] = pack4(b[0], b[1], b[2], b[3]);
+				}
+				if (ci < n_chunks) dst[ci] = make_uint4(o[0], o[1], o[2], o[3]);
+			}
+		}
+	} else {
+		// 8 bf16 in -> 8 bytes out per chunk
+		uint2 *dst = reinterpret_cast<uint2 *>(p.out + u64(row) * p.out_stride);
+		f32 const post = MODE == RMS_BF16_FIXED ? 8.0f : 1.0f;
+#pragma unroll
+		for (u32 s = 0; s < MAX_CHUNKS; ++s) {
+			if (s < per_lane) {
+				u32 const ci = s * 32 + lane;
+				u32 const wds[4] = {regs[s].x, regs[s].y, regs[s].z, regs[s].w};
+				u32 b[8];
+#pragma unroll
+				for (u32 i = 0; i < 4; ++i) {
+					b[2 * i] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(bf16_lo(wds[i]), mul), post)));
+					b[2 * i + 1] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(bf16_hi(wds[i]), mul), post)));
+				}
+				if (ci < n_chunks) {
+					dst[ci] = make_uint2(pack4(b[0], b[1], b[2], b[3]), pack4(b[4], b[5], b[6], b[7]));
+				}
+			}
+		}
+	}
+}
+
+}  // namespace x17

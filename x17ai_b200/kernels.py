@@ -1,0 +1,273 @@
+"""Host-side mirror of the reference's kernel launchers for the hot path.
+
+AttnKernelConfig / AttnKernel   <- src/device/cuda/attn.rs:45-232, launch :353-447
+GemmConfig / epilogue configs   <- src/device/cuda/gemm.rs:60-366, launch :591-641
+shape checks                    <- src/device/cuda/tensor_check.rs:19-101 (same messages)
+scale constants of the block    <- src/main.rs:412-421,464-476,548-557,599-608,650-660
+
+Tensors are torch CUDA tensors used as plain device buffers (pointer, shape, dtype); all
+arithmetic happens in libx17ai_b200.so.
+"""
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import X17Error, check
+
+DTYPE_E4M3, DTYPE_INT8, DTYPE_BF16, DTYPE_F32, DTYPE_I32_RAW = 0x30, 0x31, 0x40, 0x50, 0x51
+EPI_SCALE, EPI_RMS_NORM, EPI_GEGLU, EPI_RESIDUAL = 0, 1, 2, 3
+RMS_E4M3_FIXED, RMS_BF16_FIXED, RMS_BF16_ROWSCALE = 0, 1, 2
+FIXED_I8_SCALE = 8.0
+GELU_VAR_FIX_2 = 1.0 / ((1.0 / 3.0) + (0.5 / math.pi) * (1.0 / math.sqrt(3.0)))
+
+_TORCH_DTYPES = {
+    DTYPE_INT8: (torch.int8,),
+    DTYPE_E4M3: (torch.uint8, torch.float8_e4m3fn),
+    DTYPE_BF16: (torch.bfloat16,),
+    DTYPE_F32: (torch.float32,),
+    DTYPE_I32_RAW: (torch.int32,),
+}
+_DTYPE_NAMES = {DTYPE_INT8: "i8", DTYPE_E4M3: "e4m3", DTYPE_BF16: "bf16", DTYPE_F32: "f32", DTYPE_I32_RAW: "i32"}
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def matrix_shape(op, name, t, expected, dtype):
+    """tensor_check::matrix_shape (tensor_check.rs:19-60)."""
+    shape = tuple(t.shape)
+    if len(shape) != 2:
+        raise X17Error(f"{op} input {name} must be 2D, got shape {list(shape)}")
+    rows, cols = shape
+    if rows == 0 or cols == 0:
+        raise X17Error(f"{op} input {name} has zero size {list(shape)}")
+    if expected[0] is not None and rows != expected[0]:
+        raise X17Error(f"{op} input {name} has {rows} rows, but should have {expected[0]}")
+    if expected[1] is not None and cols != expected[1]:
+        raise X17Error(f"{op} input {name} has {cols} columns, but should have {expected[1]}")
+    _dtype_and_device(op, name, t, dtype)
+    return rows, cols
+
+
+def vector_shape(op, name, t, expected_len, dtype):
+    """tensor_check::vector_shape (tensor_check.rs:62-82)."""
+    shape = tuple(t.shape)
+    if shape not in ((expected_len,), (expected_len, 1)):
+        raise X17Error(f"{op} input {name} must have shape [{expected_len}] or [{expected_len}, 1], got {list(shape)}")
+    _dtype_and_device(op, name, t, dtype)
+
+
+def _dtype_and_device(op, name, t, dtype):
+    if t.dtype not in _TORCH_DTYPES[dtype]:
+        raise X17Error(f"{op} input {name} has dtype {t.dtype}, but should have {_DTYPE_NAMES[dtype]}")
+    if not t.is_cuda:
+        raise X17Error(f"{op} input {name} is not on device cuda")
+    if not t.is_contiguous():
+        raise X17Error(f"{op} input {name} must be contiguous")
+
+
+@dataclass(frozen=True)
+class AttnKernelConfig:
+    """attn.rs:45-53 (dtype is always Int8)."""
+    n_heads: int
+    head_dim: int
+    q_stride: int
+    kv_stride: int
+    o_stride: int
+
+    def n_ops(self, seq_len: int, window_size: int) -> float:
+        """The reference's own work count (attn.rs:72-84)."""
+        attended = window_size + 1.0 if window_size > 0 else seq_len / 2.0 + 0.5
+        return 4.0 * (self.n_heads * self.head_dim) * seq_len * attended
+
+    def _c(self):
+        return _lib.AttnConfig(self.n_heads, self.head_dim, self.q_stride, self.kv_stride, self.o_stride)
+
+
+class AttnKernel:
+    """AttnKernel::new + launch (attn.rs:171-232, 353-447). `q`, `kv`, `out` may carry a leading
+    batch dimension ([B, S, cols]); the reference's 2-D call is batch 1."""
+
+    def __init__(self, config: AttnKernelConfig):
+        self.config = config
+        self._lib = _lib.load()
+        meta = _lib.AttnMeta()
+        cfg = config._c()
+        check(self._lib.x17ai_b200_attn_meta(ctypes.byref(cfg), ctypes.byref(meta)))
+        self.THREADS_PER_BLOCK = int(meta.threads_per_block)
+        self.SMEM_BYTES = int(meta.smem_bytes)
+        self.Q_PER_BLOCK = int(meta.q_per_block)
+
+    def _shapes(self, q, kv, sink_k, sink_v, attn_temperature, out, l):
+        c = self.config
+        batch = 1
+        if q.dim() == 3:
+            batch = q.shape[0]
+            q2, kv2, out2 = q[0], kv[0], out[0]
+            if kv.shape[0] != batch or out.shape[0] != batch:
+                raise X17Error("attention inputs q, kv, out must share the batch dimension")
+        else:
+            q2, kv2, out2 = q, kv, out
+        seq_len, _ = matrix_shape("attention", "q", q2, (None, c.q_stride), DTYPE_INT8)
+        matrix_shape("attention", "kv", kv2, (seq_len, c.kv_stride), DTYPE_INT8)
+        matrix_shape("attention", "sink_k", sink_k, (c.n_heads, c.head_dim), DTYPE_INT8)
+        matrix_shape("attention", "sink_v", sink_v, (c.n_heads, c.head_dim), DTYPE_INT8)
+        vector_shape("attention", "attn_temperature", attn_temperature, c.n_heads, DTYPE_F32)
+        matrix_shape("attention", "out", out2, (seq_len, c.o_stride), DTYPE_INT8)
+        if l is not None:
+            l2 = l[0] if l.dim() == 3 else l
+            matrix_shape("attention", "l", l2, (c.n_heads, seq_len), DTYPE_F32)
+        for t in (q, kv, out):
+            if not t.is_contiguous():
+                raise X17Error("attention batched inputs must be contiguous")
+        return batch, seq_len
+
+    def launch(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l=None, window_size=0):
+        batch, seq_len = self._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
+        cfg = self.config._c()
+        check(self._lib.x17ai_b200_attn_fwd_i8(
+            stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
+            _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
+
+    def launch_debug(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, dbg_s, dbg_p, dbg_o):
+        batch, seq_len = self._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
+        cfg = self.config._c()
+        check(self._lib.x17ai_b200_attn_fwd_i8_debug(
+            stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
+            _ptr(attn_temperature), _ptr(out), _ptr(l), window_size, _ptr(dbg_s), _ptr(dbg_p), _ptr(dbg_o)))
+
+    def decode(self, stream, q, kv_cache, kv_len, sink_k, sink_v, attn_temperature, out, l=None, window_size=0,
+               kv_lens=None, n_splits=0):
+        """One new token per sequence: q [B, q_stride], kv_cache [B, T, kv_stride], out [B, o_stride]."""
+        c = self.config
+        batch, _ = matrix_shape("decode", "q", q, (None, c.q_stride), DTYPE_INT8)
+        if kv_cache.dim() != 3 or kv_cache.shape[0] != batch or kv_cache.shape[2] != c.kv_stride:
+            raise X17Error(f"decode input kv_cache must have shape [{batch}, T, {c.kv_stride}], got {list(kv_cache.shape)}")
+        _dtype_and_device("decode", "kv_cache", kv_cache, DTYPE_INT8)
+        matrix_shape("decode", "sink_k", sink_k, (c.n_heads, c.head_dim), DTYPE_INT8)
+        matrix_shape("decode", "sink_v", sink_v, (c.n_heads, c.head_dim), DTYPE_INT8)
+        vector_shape("decode", "attn_temperature", attn_temperature, c.n_heads, DTYPE_F32)
+        matrix_shape("decode", "out", out, (batch, c.o_stride), DTYPE_INT8)
+        if l is not None:
+            matrix_shape("decode", "l", l, (batch, c.n_heads), DTYPE_F32)
+        cfg = c._c()
+        check(self._lib.x17ai_b200_attn_decode_i8(
+            stream.handle, ctypes.byref(cfg), batch, _ptr(q), _ptr(kv_cache), kv_cache.shape[1], kv_len,
+            _ptr(kv_lens), _ptr(sink_k), _ptr(sink_v), _ptr(attn_temperature), _ptr(out), _ptr(l), window_size,
+            n_splits))
+
+
+@dataclass(frozen=True)
+class GemmConfig:
+    """GemmConfig + one epilogue config (gemm.rs:60-366). b is [b_rows, a_cols] (trans = true)."""
+    a_dtype: int
+    b_dtype: int
+    c_dtype: int
+    epilogue: int
+    a_cols: int
+    b_rows: int
+    inp_scale: float = 1.0
+    out_scale: float = 1.0
+    eps: float = 2.0 ** -70
+    head_dim: int = 0
+
+    def n_ops(self, a_rows: int) -> float:
+        """gemm.rs:445-449."""
+        return 2.0 * a_rows * self.a_cols * self.b_rows
+
+    def _c(self):
+        return _lib.GemmConfig(self.a_dtype, self.b_dtype, self.c_dtype, self.epilogue, self.a_cols, self.b_rows,
+                               self.inp_scale, self.out_scale, self.eps, self.head_dim)
+
+
+class GemmKernel:
+    """GemmKernel<E>::new + launch (gemm.rs:368-443, 591-641)."""
+
+    def __init__(self, config: GemmConfig):
+        self.config = config
+        self._lib = _lib.load()
+        meta = _lib.GemmMeta()
+        cfg = config._c()
+        check(self._lib.x17ai_b200_gemm_meta(ctypes.byref(cfg), ctypes.byref(meta)))
+        self.THREADS_PER_BLOCK = int(meta.threads_per_block)
+        self.SMEM_BYTES = int(meta.smem_bytes)
+        self.M_PER_BLOCK = int(meta.m_per_block)
+        self.N_PER_BLOCK = int(meta.n_per_block)
+
+    def launch(self, stream, a, b, c, rrms=None, residual=None):
+        g = self.config
+        a_rows, _ = matrix_shape("gemm", "a", a, (None, g.a_cols), g.a_dtype)
+        split = g.a_dtype == DTYPE_E4M3 and g.b_dtype == DTYPE_INT8
+        if split:  # b is the [b_rows, 2 * a_cols] e4m3 buffer made by split_i8_weights
+            matrix_shape("gemm", "b", b, (g.b_rows, 2 * g.a_cols), DTYPE_E4M3)
+        else:
+            matrix_shape("gemm", "b", b, (g.b_rows, g.a_cols), g.b_dtype)
+        c_cols = g.b_rows if g.epilogue in (EPI_SCALE, EPI_RMS_NORM) else g.b_rows // 2
+        matrix_shape("gemm", "c", c, (a_rows, c_cols), g.c_dtype)
+        if g.epilogue == EPI_RMS_NORM:
+            if rrms is None:
+                raise X17Error("gemm rms-norm epilogue needs the rrms output")
+            matrix_shape("gemm", "rrms", rrms, (a_rows, g.b_rows // (2 * g.head_dim)), DTYPE_F32)
+        if g.epilogue == EPI_RESIDUAL:
+            if residual is None:
+                raise X17Error("gemm residual epilogue needs the residual input")
+            matrix_shape("gemm", "residual", residual, (a_rows, g.b_rows // 2), DTYPE_INT8)
+        cfg = g._c()
+        check(self._lib.x17ai_b200_gemm_fwd(stream.handle, ctypes.byref(cfg), _ptr(a), a_rows, _ptr(b), g.b_rows,
+                                            _ptr(c), _ptr(rrms), _ptr(residual)))
+
+
+def split_i8_weights(stream, w):
+    """int8 weights [rows, cols] -> e4m3 [rows, 2*cols] = [16*hi | lo] for e4m3-activation GEMMs."""
+    rows, cols = matrix_shape("split_i8_weights", "w", w, (None, None), DTYPE_INT8)
+    out = torch.empty((rows, 2 * cols), dtype=torch.uint8, device=w.device)
+    check(_lib.load().x17ai_b200_split_i8_weights(stream.handle, _ptr(w), rows, cols, _ptr(out)))
+    return out
+
+
+def rms_norm(stream, mode, inp, out, row_scale=None, eps=2.0 ** -70):
+    """Rms_norm::kernel (rms_norm.cu:55-113) and its bf16-input modes."""
+    in_dtype = DTYPE_E4M3 if mode == RMS_E4M3_FIXED else DTYPE_BF16
+    rows, cols = matrix_shape("rms_norm", "inp", inp, (None, None), in_dtype)
+    matrix_shape("rms_norm", "out", out, (rows, cols), DTYPE_INT8)
+    if mode == RMS_BF16_ROWSCALE:
+        if row_scale is None:
+            raise X17Error("rms_norm row-scale mode needs the row_scale output")
+        vector_shape("rms_norm", "row_scale", row_scale, rows, DTYPE_F32)
+    check(_lib.load().x17ai_b200_rms_norm(stream.handle, mode, _ptr(inp), rows, cols, _ptr(out), _ptr(row_scale), eps))
+
+
+# ---- the live kernels of the reference's block (src/main.rs:387-675) with their scales ----------
+
+def attn_q_fwd_config(model_dim, q_outputs):
+    return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_INT8, EPI_SCALE, model_dim, q_outputs,
+                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=FIXED_I8_SCALE)
+
+
+def attn_kv_fwd_config(model_dim, kv_outputs, head_dim, eps=2.0 ** -70):
+    return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_INT8, EPI_RMS_NORM, model_dim, kv_outputs,
+                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=FIXED_I8_SCALE, eps=eps, head_dim=head_dim)
+
+
+def attn_y_fwd_config(attn_width, model_dim, c_dtype=DTYPE_E4M3):
+    return GemmConfig(DTYPE_INT8, DTYPE_INT8, c_dtype, EPI_RESIDUAL, attn_width, 2 * model_dim,
+                      inp_scale=attn_width ** -0.5 / 64.0, out_scale=1.0)
+
+
+def ffn_f_fwd_config(model_dim, f_width):
+    return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_E4M3, EPI_GEGLU, model_dim, 2 * f_width,
+                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=1.0)
+
+
+def ffn_y_fwd_f8_config(f_width, model_dim, b_dtype=DTYPE_INT8, c_dtype=DTYPE_E4M3):
+    return GemmConfig(DTYPE_E4M3, b_dtype, c_dtype, EPI_RESIDUAL, f_width, 2 * model_dim,
+                      inp_scale=math.sqrt(GELU_VAR_FIX_2 / f_width) / 8.0, out_scale=1.0)
+
+
+def ffn_y_fwd_i8_config(f_width, model_dim, c_dtype=DTYPE_INT8):
+    return GemmConfig(DTYPE_INT8, DTYPE_INT8, c_dtype, EPI_RESIDUAL, f_width, 2 * model_dim,
+                      inp_scale=math.sqrt(GELU_VAR_FIX_2 / f_width) / 64.0, out_scale=1.0)
