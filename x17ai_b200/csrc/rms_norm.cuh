@@ -37,6 +37,36 @@ constexpr u32 THREADS = WARPS * 32;
 constexpr u32 MAX_CHUNKS = 16;  // 16-byte chunks per lane held in registers
 }  // namespace rms_cfg
 
+// Two e4m3 bytes -> two f32 through the hardware e4m3x2 -> f16x2 converter. For the codes the
+// reference's encoder produces (zero and normals, cuda/utils_b8.cuh:636-647) this is exactly
+// e4m3_to_bf16 of the reference (utils_b8.cuh:652-657); 0x80 decodes to -0, which squares and
+// rounds like +0.
+X17_DEV void e4m3x2_to_f32(u32 pair16, f32 &a, f32 &b) {
+	u32 h2;
+	asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(h2) : "r"(pair16));
+	asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}"
+		: "=f"(a), "=f"(b)
+		: "r"(h2));
+}
+
+// rint(clamp(v, -127, 127)) of four f32 packed into bytes, without the conversion unit:
+// adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits (round half to even,
+// like cvt.rni), a saturating pack clamps to [-128, 127] and a byte-wise max lifts -128 to -127.
+X17_DEV u32 pack4_fixedi8(f32 v0, f32 v1, f32 v2, f32 v3) {
+	// valid for |v| < 2^22 (here |v| <= 8 * sqrt(cols))
+	constexpr f32 MAGIC = 12582912.0f;
+	constexpr i32 MAGIC_BITS = 0x4B400000;
+	i32 const i0 = __float_as_int(__fadd_rn(v0, MAGIC)) - MAGIC_BITS;
+	i32 const i1 = __float_as_int(__fadd_rn(v1, MAGIC)) - MAGIC_BITS;
+	i32 const i2 = __float_as_int(__fadd_rn(v2, MAGIC)) - MAGIC_BITS;
+	i32 const i3 = __float_as_int(__fadd_rn(v3, MAGIC)) - MAGIC_BITS;
+	// d = sat(a) << 8 | sat(b) | c << 16: build the upper half first, then shift it up
+	u32 hi, packed;
+	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(i3), "r"(i2));
+	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed) : "r"(i1), "r"(i0), "r"(hi));
+	return __vmaxs4(packed, 0x81818181u);
+}
+
 X17_DEV f32 bf16_lo(u32 w) { return __uint_as_float(w << 16); }
 X17_DEV f32 bf16_hi(u32 w) { return __uint_as_float(w & 0xFFFF0000u); }
 
@@ -56,25 +86,31 @@ rms_norm_kernel(const RmsParams p) {
 		static_cast<u8 const *>(p.inp) + u64(row) * p.inp_stride * (MODE == RMS_E4M3_FIXED ? 1 : 2));
 
 	uint4 regs[MAX_CHUNKS];
+	// all loads of the row are issued before any arithmetic
+#pragma unroll
+	for (u32 s = 0; s < MAX_CHUNKS; ++s) {
+		if (s < per_lane) {
+			u32 const ci = s * 32 + lane;
+			regs[s] = ci < n_chunks ? __ldg(src + ci) : make_uint4(0, 0, 0, 0);
+		}
+	}
 	f32 local = 0.0f;
 	f32 amax = 0.0f;
 #pragma unroll
 	for (u32 s = 0; s < MAX_CHUNKS; ++s) {
 		if (s < per_lane) {
-			u32 const ci = s * 32 + lane;
-			uint4 v = make_uint4(0, 0, 0, 0);
-			if (ci < n_chunks) v = __ldg(src + ci);
-			regs[s] = v;
-			u32 const wds[4] = {v.x, v.y, v.z, v.w};
+			u32 const wds[4] = {regs[s].x, regs[s].y, regs[s].z, regs[s].w};
 			f32 acc = 0.0f;
 #pragma unroll
 			for (u32 i = 0; i < 4; ++i) {
 				if constexpr (MODE == RMS_E4M3_FIXED) {
-#pragma unroll
-					for (u32 j = 0; j < 4; ++j) {
-						f32 x = e4m3_to_f32((wds[i] >> (8 * j)) & 0xFFu);
-						acc = __fmaf_rn(x, x, acc);
-					}
+					f32 x0, x1, x2, x3;
+					e4m3x2_to_f32(wds[i] & 0xFFFFu, x0, x1);
+					e4m3x2_to_f32(wds[i] >> 16, x2, x3);
+					acc = __fmaf_rn(x0, x0, acc);
+					acc = __fmaf_rn(x1, x1, acc);
+					acc = __fmaf_rn(x2, x2, acc);
+					acc = __fmaf_rn(x3, x3, acc);
 				} else {
 					f32 x0 = bf16_lo(wds[i]), x1 = bf16_hi(wds[i]);
 					acc = __fmaf_rn(x0, x0, acc);
@@ -100,6 +136,8 @@ rms_norm_kernel(const RmsParams p) {
 		if (lane == 0) p.row_scale[row] = scale;
 		mul = scale > 0.0f ? __fdiv_rn(rrms, scale) : 0.0f;
 	}
+	// (x * rrms) * 8 == x * (rrms * 8) exactly: 8 is a power of two
+	f32 const mul8 = MODE == RMS_BF16_ROWSCALE ? mul : __fmul_rn(mul, 8.0f);
 
 	if constexpr (MODE == RMS_E4M3_FIXED) {
 		uint4 *dst = reinterpret_cast<uint4 *>(p.out + u64(row) * p.out_stride);
@@ -111,13 +149,11 @@ rms_norm_kernel(const RmsParams p) {
 				u32 o[4];
 #pragma unroll
 				for (u32 i = 0; i < 4; ++i) {
-					u32 b[4];
-#pragma unroll
-					for (u32 j = 0; j < 4; ++j) {
-						f32 x = e4m3_to_f32((wds[i] >> (8 * j)) & 0xFFu);
-						b[j] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(x, mul), 8.0f)));
-					}
-					o[i] = pack4(b[0], b[1], b[2], b[3]);
+					f32 x0, x1, x2, x3;
+					e4m3x2_to_f32(wds[i] & 0xFFFFu, x0, x1);
+					e4m3x2_to_f32(wds[i] >> 16, x2, x3);
+					o[i] = pack4_fixedi8(__fmul_rn(x0, mul8), __fmul_rn(x1, mul8), __fmul_rn(x2, mul8),
+										 __fmul_rn(x3, mul8));
 				}
 				if (ci < n_chunks) dst[ci] = make_uint4(o[0], o[1], o[2], o[3]);
 			}
@@ -125,21 +161,16 @@ rms_norm_kernel(const RmsParams p) {
 	} else {
 		// 8 bf16 in -> 8 bytes out per chunk
 		uint2 *dst = reinterpret_cast<uint2 *>(p.out + u64(row) * p.out_stride);
-		f32 const post = MODE == RMS_BF16_FIXED ? 8.0f : 1.0f;
 #pragma unroll
 		for (u32 s = 0; s < MAX_CHUNKS; ++s) {
 			if (s < per_lane) {
 				u32 const ci = s * 32 + lane;
 				u32 const wds[4] = {regs[s].x, regs[s].y, regs[s].z, regs[s].w};
-				u32 b[8];
-#pragma unroll
-				for (u32 i = 0; i < 4; ++i) {
-					b[2 * i] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(bf16_lo(wds[i]), mul), post)));
-					b[2 * i + 1] = u32(f32_to_fixedi8(__fmul_rn(__fmul_rn(bf16_hi(wds[i]), mul), post)));
-				}
-				if (ci < n_chunks) {
-					dst[ci] = make_uint2(pack4(b[0], b[1], b[2], b[3]), pack4(b[4], b[5], b[6], b[7]));
-				}
+				u32 const o0 = pack4_fixedi8(__fmul_rn(bf16_lo(wds[0]), mul8), __fmul_rn(bf16_hi(wds[0]), mul8),
+											 __fmul_rn(bf16_lo(wds[1]), mul8), __fmul_rn(bf16_hi(wds[1]), mul8));
+				u32 const o1 = pack4_fixedi8(__fmul_rn(bf16_lo(wds[2]), mul8), __fmul_rn(bf16_hi(wds[2]), mul8),
+											 __fmul_rn(bf16_lo(wds[3]), mul8), __fmul_rn(bf16_hi(wds[3]), mul8));
+				if (ci < n_chunks) dst[ci] = make_uint2(o0, o1);
 			}
 		}
 	}
