@@ -140,9 +140,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 	u32 const o_full_bar = bar_base + 8 * (2 * STAGES + 1);
 	auto s_full_bar = [&](u32 b) { return bar_base + 8 * (2 * STAGES + 2 + b); };
 	auto s_done_bar = [&](u32 b) { return bar_base + 8 * (2 * STAGES + 4 + b); };
-	u32 const tmem_slot = bar_base + 8 * (2 * STAGES + 6);
+	u32 const p_ready_bar = bar_base + 8 * (2 * STAGES + 6);
+	u32 const pv_done_bar = bar_base + 8 * (2 * STAGES + 7);
+	u32 const tmem_slot = bar_base + 8 * (2 * STAGES + 8);
 	volatile u32 *const tmem_slot_gen =
-		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 6));
+		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 8));
 	volatile u32 *const abort_flag = tmem_slot_gen + 1;
 	WaitCtx const ctx{abort_flag, p.status};
 
@@ -171,6 +173,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			mbar_init(s_full_bar(b), 1);
 			mbar_init(s_done_bar(b), ROW_THREADS);
 		}
+		mbar_init(p_ready_bar, ROW_THREADS);
+		mbar_init(pv_done_bar, 1);
 		*abort_flag = 0;
 		mbar_fence_init();
 	}
@@ -192,21 +196,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			tma_load_3d(s_q, &tm_q, q_full_bar, i32(head * D), i32(q0), i32(batch));
 			u32 it = 0;
 			bool ok = true;
-			for (u32 sweep = 0; sweep < 2 && ok; ++sweep) {
-				for (u32 t = t_begin; t <= t_end && ok; ++t) {
-					u32 const n_items = sweep == 0 ? 1u : 2u;  // K only, then K and V
-					for (u32 item = 0; item < n_items; ++item, ++it) {
-						u32 const s = it % STAGES;
-						u32 const ph = (it / STAGES) & 1;
-						if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, ST_WAIT_STAGE_EMPTY, s)) {
-							ok = false;
-							break;
-						}
-						mbar_expect_tx(full_bar(s), TILE_BYTES);
-						tma_load_3d(s_ring + s * TILE_BYTES, &tm_kv, full_bar(s),
-									i32(2 * head * D + item * D), i32(t * BKV), i32(batch));
-					}
-				}
+			// one ring entry: the K (item 0) or V (item 1) tile of KV tile t
+			auto load = [&](u32 t, u32 item) -> bool {
+				u32 const s = it % STAGES;
+				u32 const ph = (it / STAGES) & 1;
+				if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, ST_WAIT_STAGE_EMPTY, s)) return false;
+				mbar_expect_tx(full_bar(s), TILE_BYTES);
+				tma_load_3d(s_ring + s * TILE_BYTES, &tm_kv, full_bar(s), i32(2 * head * D + item * D),
+							i32(t * BKV), i32(batch));
+				++it;
+				return true;
+			};
+			// sweep 1: K tiles. sweep 2, in the order the MMA warp consumes them:
+			// K[first], then K[t+1] before V[t] (Q.K^T of the next tile is issued ahead of P.V)
+			for (u32 t = t_begin; t <= t_end && ok; ++t) ok = load(t, 0);
+			if (ok) ok = load(t_begin, 0);
+			for (u32 t = t_begin; t <= t_end && ok; ++t) {
+				if (t < t_end) ok = load(t + 1, 0);
+				if (ok) ok = load(t, 1);
 			}
 		}
 	} else if (warp == 1) {
@@ -219,7 +226,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			u32 it = 0;
 			u32 uses[2] = {0, 0};  // Q.K^T tiles issued into S buffer b so far
 
-			// O += P.V for one tile; P of that tile is complete (its s_done has been observed)
+			auto issue_qk = [&](u32 b) -> bool {
+				u32 const s = it % STAGES;
+				u32 const ph = (it / STAGES) & 1;
+				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
+				tc_fence_after();
+				u64 const adesc = make_smem_desc(s_q, D);
+				u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+#pragma unroll
+				for (u32 ks = 0; ks < D / 32; ++ks) {
+					mma_i8_ss(tmem_base + b * BKV, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
+				}
+				tc_commit(empty_bar(s));
+				tc_commit(s_full_bar(b));
+				++it;
+				++uses[b];
+				return true;
+			};
+			// O += P.V for one tile; P of that tile is in shared memory
 			auto issue_pv = [&](bool first) -> bool {
 				u32 const s = it % STAGES;
 				u32 const ph = (it / STAGES) & 1;
@@ -235,50 +259,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 							  (!first || ks != 0) ? 1u : 0u);
 				}
 				tc_commit(empty_bar(s));
+				tc_commit(pv_done_bar);
 				++it;
 				return true;
 			};
-
-			for (u32 sweep = 0; sweep < 2 && ok; ++sweep) {
-				for (u32 t = t_begin; t <= t_end && ok; ++t) {
-					u32 const b = sweep == 0 ? ((t - t_begin) & 1u) : 0u;
-					if (uses[b] > 0) {  // the previous contents of S_b have been consumed
-						if (!mbar_wait(s_done_bar(b), (uses[b] - 1) & 1, ctx, ST_WAIT_S_DONE, t)) {
-							ok = false;
-							break;
-						}
-						tc_fence_after();
-					}
-					if (sweep == 1 && t > t_begin) {  // the same event: P of tile t-1 is written
-						if (!issue_pv(t - 1 == t_begin)) {
-							ok = false;
-							break;
-						}
-					}
-					// S_b = Q . K^T
-					u32 const s = it % STAGES;
-					u32 const ph = (it / STAGES) & 1;
-					if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) {
-						ok = false;
-						break;
-					}
-					tc_fence_after();
-					u64 const adesc = make_smem_desc(s_q, D);
-					u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
-#pragma unroll
-					for (u32 ks = 0; ks < D / 32; ++ks) {
-						mma_i8_ss(tmem_base + b * BKV, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
-					}
-					tc_commit(empty_bar(s));
-					tc_commit(s_full_bar(b));
-					++it;
-					++uses[b];
-				}
-			}
-			if (ok && mbar_wait(s_done_bar(0), (uses[0] - 1) & 1, ctx, ST_WAIT_S_DONE, t_end)) {
+			// before S_b is overwritten, its previous contents must have been read
+			auto wait_s_read = [&](u32 b, u32 t) -> bool {
+				if (uses[b] == 0) return true;
+				if (!mbar_wait(s_done_bar(b), (uses[b] - 1) & 1, ctx, ST_WAIT_S_DONE, t)) return false;
 				tc_fence_after();
-				if (issue_pv(t_end == t_begin)) tc_commit(o_full_bar);
+				return true;
+			};
+
+			// sweep 1: the scores ping-pong between the two halves of the allocation
+			for (u32 t = t_begin; t <= t_end && ok; ++t) {
+				u32 const b = (t - t_begin) & 1u;
+				ok = wait_s_read(b, t) && issue_qk(b);
 			}
+			// sweep 2: S lives in buffer 0 only; the rows copy it to registers and release it at
+			// once, so Q.K^T of tile t+1 runs while they work on tile t
+			if (ok) ok = wait_s_read(0, t_begin) && issue_qk(0);
+			u32 n_p = 0;
+			for (u32 t = t_begin; t <= t_end && ok; ++t) {
+				if (t < t_end) ok = wait_s_read(0, t) && issue_qk(0);
+				if (!ok) break;
+				if (!mbar_wait(p_ready_bar, n_p & 1, ctx, ST_WAIT_S_DONE, 0x100u + t)) {
+					ok = false;
+					break;
+				}
+				++n_p;
+				tc_fence_after();
+				ok = issue_pv(t == t_begin);
+			}
+			if (ok) tc_commit(o_full_bar);
 		}
 	} else {
 		// ---------------- two threads per query row ----------------
@@ -414,6 +427,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			tmem_ld_32x32b_x32(ta, r0);
 			tmem_ld_32x32b_x32(ta + 32, r1);
 			tmem_wait_ld();
+			tc_fence_before();
+			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
 			u32 pk0[8], pk1[8];
 			if (edge) {
 				softmax_chunk<true>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
@@ -422,13 +437,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				softmax_chunk<false>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
 				softmax_chunk<false>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
+			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
+				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
+					ok = false;
+					break;
+				}
+			}
 			st_shared_v4(p_row + (((ch0 + 0) ^ sw) << 4), pk0[0], pk0[1], pk0[2], pk0[3]);
 			st_shared_v4(p_row + (((ch0 + 1) ^ sw) << 4), pk0[4], pk0[5], pk0[6], pk0[7]);
 			st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
 			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
 			fence_proxy_async_smem();
-			tc_fence_before();
-			mbar_arrive(s_done_bar(0));
+			mbar_arrive(p_ready_bar);
 			if constexpr (DEBUG) {
 				if (row_ok) {
 					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len

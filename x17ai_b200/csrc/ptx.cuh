@@ -112,22 +112,25 @@ X17_DEV void mbar_expect_tx(u32 bar, u32 bytes) {
 X17_DEV void mbar_arrive(u32 bar) {
 	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One try: the thread may be suspended by the hardware for up to `SUSPEND_NS` while the phase
+// is incomplete, which keeps waiting warps from burning issue slots on a polling loop.
+constexpr u32 SUSPEND_NS = 20000;
 X17_DEV bool mbar_try_wait(u32 bar, u32 parity) {
 	u32 ok;
 	asm volatile(
 		"{\n\t.reg .pred P;\n\t"
-		"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+		"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
 		"selp.u32 %0, 1, 0, P;\n\t}"
 		: "=r"(ok)
-		: "r"(bar), "r"(parity)
+		: "r"(bar), "r"(parity), "r"(SUSPEND_NS)
 		: "memory");
 	return ok != 0;
 }
 
 // Bounded wait: returns false when it gives up (after about a second), having set the CTA's
 // abort flag so that the other roles leave their waits quickly too.
-constexpr u32 WAIT_FAST_POLLS = 1u << 14;
-constexpr u32 WAIT_SLOW_POLLS = 1u << 22;  // x >= 64 ns sleep: about a second at least
+constexpr u32 WAIT_FAST_POLLS = 1u << 10;
+constexpr u32 WAIT_SLOW_POLLS = 1u << 17;  // x up to 20 us of suspension each: a second or two
 
 X17_DEV bool mbar_wait(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 detail) {
 	for (u32 i = 0; i < WAIT_FAST_POLLS; ++i) {
@@ -136,7 +139,6 @@ X17_DEV bool mbar_wait(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 de
 	for (u32 i = 0; i < WAIT_SLOW_POLLS; ++i) {
 		if (mbar_try_wait(bar, parity)) return true;
 		if (*ctx.abort_flag != 0) return false;
-		__nanosleep(64);
 	}
 	*ctx.abort_flag = 1;
 	report_status(ctx.status, code, detail);
