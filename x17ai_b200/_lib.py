@@ -8,7 +8,10 @@ from ctypes import (POINTER, Structure, c_char_p, c_double, c_float, c_int, c_in
                     c_uint32, c_uint64, c_uint8, c_void_p)
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libx17ai_b200.so"
+import os
+
+# X17AI_B200_LIB overrides the in-tree library (an alternative build of the same sources)
+LIB_PATH = Path(os.environ.get("X17AI_B200_LIB") or (Path(__file__).resolve().parent / "libx17ai_b200.so"))
 
 
 class X17Error(RuntimeError):

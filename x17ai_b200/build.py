@@ -28,6 +28,8 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    if os.environ.get("X17AI_B200_LIB"):
+        return Path(os.environ["X17AI_B200_LIB"])
     if not force and not needs_build():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

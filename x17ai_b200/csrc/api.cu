@@ -405,6 +405,16 @@ size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_
 	return buf.len;
 }
 
+#ifdef X17_EXPERIMENT_TIMING
+// experiment builds only: copies the recorded timeline to the host
+int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
+	cudaDeviceSynchronize();
+	cudaError_t e = cudaMemcpyFromSymbol(times, x17::g_times, sizeof(long long) * 4 * 128);
+	if (e == cudaSuccess) e = cudaMemcpyFromSymbol(counts, x17::g_ntimes, sizeof(unsigned) * 4);
+	return int(e);
+}
+#endif
+
 uint64_t x17ai_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 x17ai_DiagnosticBuffer *x17ai_b200_read_status(x17ai_CudaStreamHandle *stream, uint32_t status[4]) {

@@ -62,7 +62,11 @@ constexpr u32 O_COL = 128;
 constexpr u32 XCHG_BYTES = ROW_THREADS * 4;
 template <u32 D>
 constexpr u32 smem_bytes() {
+#ifdef X17_EXPERIMENT_TIMING
+	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256 + 4096;
+#else
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
+#endif
 }
 constexpr f32 MAGIC = 12582912.0f;  // 1.5 * 2^23
 constexpr u32 MAGIC_BITS = 0x4B400000u;
@@ -91,7 +95,11 @@ X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u3
 			if constexpr (EDGE) {
 				x = (col0 + i - lo) < span ? x : -INFINITY;
 			}
+#ifdef X17_EXPERIMENT_NO_EX2
+			f32 const ex = x * 1e-9f + 0.5f;
+#else
 			f32 const ex = ex2_approx(x);
+#endif
 			sum[e] = __fadd_rn(sum[e], ex);
 			// rint(255 * ex) lands in the low mantissa byte
 			q4[e] = __float_as_uint(__fmaf_rn(ex, 255.0f, MAGIC));
@@ -100,6 +108,53 @@ X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u3
 		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
 		pk[g] = __byte_perm(lo2, hi2, 0x5410);
 	}
+}
+
+// Same arithmetic, same roundings, with the four f32 operations per element issued as packed
+// f32x2 instructions (two elements per issue slot).
+template <bool EDGE>
+X17_DEV void softmax_chunk_v2(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
+							  f32 (&sum)[4], u32 (&pk)[8]) {
+	using namespace attn_cfg;
+	u64 const neg_magic2 = pack_f32x2(-MAGIC, -MAGIC);
+	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
+	u64 const temp2 = pack_f32x2(temp, temp);
+	u64 const negm2 = pack_f32x2(neg_m, neg_m);
+	u64 const s255 = pack_f32x2(255.0f, 255.0f);
+	u64 sum01 = pack_f32x2(sum[0], sum[1]);
+	u64 sum23 = pack_f32x2(sum[2], sum[3]);
+#pragma unroll
+	for (u32 g = 0; g < 8; ++g) {
+		u32 q4[4];
+#pragma unroll
+		for (u32 h = 0; h < 2; ++h) {
+			u32 const i = 4 * g + 2 * h;
+			// exact int -> float without the conversion unit (|acc| < 2^22)
+			u64 const f2 = add_f32x2(pack_f32x2(__uint_as_float(r[i] + MAGIC_BITS), __uint_as_float(r[i + 1] + MAGIC_BITS)),
+									 neg_magic2);
+			u64 const x2 = fma_f32x2(f2, temp2, negm2);
+			f32 x0, x1;
+			unpack_f32x2(x2, x0, x1);
+			if constexpr (EDGE) {
+				x0 = (col0 + i - lo) < span ? x0 : -INFINITY;
+				x1 = (col0 + i + 1 - lo) < span ? x1 : -INFINITY;
+			}
+			u64 const e2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+			if (h == 0) sum01 = add_f32x2(sum01, e2);
+			else sum23 = add_f32x2(sum23, e2);
+			// rint(255 * ex) lands in the low mantissa byte
+			u64 const q2 = fma_f32x2(e2, s255, magic2);
+			f32 qa, qb;
+			unpack_f32x2(q2, qa, qb);
+			q4[2 * h] = __float_as_uint(qa);
+			q4[2 * h + 1] = __float_as_uint(qb);
+		}
+		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
+		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
+		pk[g] = __byte_perm(lo2, hi2, 0x5410);
+	}
+	unpack_f32x2(sum01, sum[0], sum[1]);
+	unpack_f32x2(sum23, sum[2], sum[3]);
 }
 
 template <bool EDGE, bool WANT_MAX>
@@ -114,6 +169,22 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 		ext[i & 3] = WANT_MAX ? max(ext[i & 3], v) : min(ext[i & 3], v);
 	}
 }
+
+#ifdef X17_EXPERIMENT_TIMING
+// timeline of one CTA, recorded in shared memory and copied out at the end:
+// g_times[role][event] = clock64() << 8 | tag; roles: 0 TMA, 1 MMA, 2 row warp 2, 3 row warp 6
+__device__ long long g_times[4][128];
+__device__ unsigned g_ntimes[4];
+#define X17_T(role, tag)                                                       \
+	do {                                                                       \
+		if ((threadIdx.x & 31) == 0 && t_n < 127) {                            \
+			t_buf[(role) * 128 + t_n] = (clock64() << 8) | (tag);              \
+			++t_n;                                                             \
+		}                                                                      \
+	} while (0)
+#else
+#define X17_T(role, tag) do {} while (0)
+#endif
 
 template <u32 D, bool DEBUG>
 __global__ void __launch_bounds__(attn_cfg::THREADS, 2)
@@ -147,6 +218,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 8));
 	volatile u32 *const abort_flag = tmem_slot_gen + 1;
 	WaitCtx const ctx{abort_flag, p.status};
+#ifdef X17_EXPERIMENT_TIMING
+	long long *const t_buf = reinterpret_cast<long long *>(smem_gen + BAR_OFF + 256);
+	u32 t_n = 0;
+#endif
 
 	u32 const warp = threadIdx.x >> 5;
 	u32 const lane = threadIdx.x & 31;
@@ -205,6 +280,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				tma_load_3d(s_ring + s * TILE_BYTES, &tm_kv, full_bar(s), i32(2 * head * D + item * D),
 							i32(t * BKV), i32(batch));
 				++it;
+				X17_T(0, 1);
 				return true;
 			};
 			// sweep 1: K tiles. sweep 2, in the order the MMA warp consumes them:
@@ -224,23 +300,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			u32 const o_tmem = tmem_base + O_COL;
 			bool ok = mbar_wait(q_full_bar, 0, ctx, ST_WAIT_Q_FULL, 0);
 			u32 it = 0;
-			u32 uses[2] = {0, 0};  // Q.K^T tiles issued into S buffer b so far
+			u32 use0 = 0, use1 = 0;  // Q.K^T tiles issued into S buffer 0 / 1 so far
+			u64 const q_desc = make_smem_desc(s_q, D);
+			u64 const p_desc = make_smem_desc(s_p, 128);
+			u64 const ring_desc = make_smem_desc(s_ring, D);  // + stage * (TILE_BYTES >> 4)
 
 			auto issue_qk = [&](u32 b) -> bool {
 				u32 const s = it % STAGES;
 				u32 const ph = (it / STAGES) & 1;
 				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
 				tc_fence_after();
-				u64 const adesc = make_smem_desc(s_q, D);
-				u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+				X17_T(1, 5);
+				u64 const bdesc = ring_desc + u64(s * (TILE_BYTES >> 4));
 #pragma unroll
 				for (u32 ks = 0; ks < D / 32; ++ks) {
-					mma_i8_ss(tmem_base + b * BKV, adesc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
+					mma_i8_ss(tmem_base + b * BKV, q_desc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
 				}
+				X17_T(1, 6);
 				tc_commit(empty_bar(s));
 				tc_commit(s_full_bar(b));
 				++it;
-				++uses[b];
+				use0 += b == 0 ? 1u : 0u;
+				use1 += b == 0 ? 0u : 1u;
+				X17_T(1, 2);
 				return true;
 			};
 			// O += P.V for one tile; P of that tile is in shared memory
@@ -249,25 +331,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				u32 const ph = (it / STAGES) & 1;
 				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
 				tc_fence_after();
-				u64 const adesc = make_smem_desc(s_p, 128);
-				u64 const bdesc = make_smem_desc(s_ring + s * TILE_BYTES, D);
+				X17_T(1, 5);
+				u64 const bdesc = ring_desc + u64(s * (TILE_BYTES >> 4));
 #pragma unroll
 				for (u32 ks = 0; ks < BKV / 32; ++ks) {
 					// A: +32 bytes along the key axis inside the swizzle row;
 					// B (MN-major): +32 key rows of D bytes each
-					mma_i8_ss(o_tmem, adesc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
+					mma_i8_ss(o_tmem, p_desc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
 							  (!first || ks != 0) ? 1u : 0u);
 				}
+				X17_T(1, 6);
 				tc_commit(empty_bar(s));
 				tc_commit(pv_done_bar);
 				++it;
+				X17_T(1, 4);
 				return true;
 			};
 			// before S_b is overwritten, its previous contents must have been read
 			auto wait_s_read = [&](u32 b, u32 t) -> bool {
-				if (uses[b] == 0) return true;
-				if (!mbar_wait(s_done_bar(b), (uses[b] - 1) & 1, ctx, ST_WAIT_S_DONE, t)) return false;
+				u32 const used = b == 0 ? use0 : use1;
+				if (used == 0) return true;
+				if (!mbar_wait(s_done_bar(b), (used - 1) & 1, ctx, ST_WAIT_S_DONE, t)) return false;
 				tc_fence_after();
+				X17_T(1, 1);
 				return true;
 			};
 
@@ -289,6 +375,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				}
 				++n_p;
 				tc_fence_after();
+				X17_T(1, 3);
 				ok = issue_pv(t == t_begin);
 			}
 			if (ok) tc_commit(o_full_bar);
@@ -329,9 +416,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		bool const pos_t = head_t >= 0.0f;  // uniform over the CTA; row_t > 0 always
 		f32 const sink_s = __fmul_rn(__int2float_rn(sink_dot), temp);
 
-		u32 uses[2] = {0, 0};
+		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
 		bool ok = true;
 		u32 const col_base = half * 64u;
+#ifdef X17_EXPERIMENT_TIMING
+		u32 const trole = warp == 2 ? 2u : 3u;
+		bool const tme = warp == 2 || warp == 6;
+#define X17_TR(tag) do { if (tme) X17_T(trole, tag); } while (0)
+#else
+#define X17_TR(tag) do {} while (0)
+#endif
 
 		// visible columns of this row inside tile k0: lo <= col < lo + span (only used on edge tiles)
 		auto visible = [&](u32 k0, u32 &lo, u32 &span) {
@@ -347,12 +441,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		for (u32 i = 0; i < 4; ++i) ext[i] = pos_t ? INT32_MIN : INT32_MAX;
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			u32 const b = (t - t_begin) & 1u;
-			if (!mbar_wait_warp(s_full_bar(b), uses[b] & 1, ctx, ST_WAIT_S_FULL, t)) {
+			u32 const par = b == 0 ? (use0 & 1u) : (use1 & 1u);
+			if (!mbar_wait_warp(s_full_bar(b), par, ctx, ST_WAIT_S_FULL, t)) {
 				ok = false;
 				break;
 			}
-			++uses[b];
+			use0 += b == 0 ? 1u : 0u;
+			use1 += b == 0 ? 0u : 1u;
 			tc_fence_after();
+			X17_TR(1);
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
@@ -364,6 +461,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
+			X17_TR(2);
 			if (edge) {
 				if (pos_t) {
 					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
@@ -412,12 +510,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		u32 const sw = row & 7u;
 		u32 const ch0 = half * 4u;  // first of this thread's four 16-byte chunks
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
-			if (!mbar_wait_warp(s_full_bar(0), uses[0] & 1, ctx, ST_WAIT_S_FULL, t)) {
+			if (!mbar_wait_warp(s_full_bar(0), use0 & 1, ctx, ST_WAIT_S_FULL, t)) {
 				ok = false;
 				break;
 			}
-			++uses[0];
+			++use0;
 			tc_fence_after();
+			X17_TR(3);
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
@@ -429,14 +528,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
+			X17_TR(4);
 			u32 pk0[8], pk1[8];
 			if (edge) {
-				softmax_chunk<true>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk<true>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk_v2<true>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk_v2<true>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			} else {
-				softmax_chunk<false>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk<false>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk_v2<false>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk_v2<false>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
+			X17_TR(5);
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
 				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
 					ok = false;
@@ -449,6 +550,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
 			fence_proxy_async_smem();
 			mbar_arrive(p_ready_bar);
+			X17_TR(6);
 			if constexpr (DEBUG) {
 				if (row_ok) {
 					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
@@ -468,8 +570,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		named_barrier_sync(1, ROW_THREADS);
 		f32 const other = xchg[xpartner];
 		f32 const both = half == 0 ? __fadd_rn(part, other) : __fadd_rn(other, part);
+		X17_TR(7);
 		if (ok && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
 			tc_fence_after();
+			X17_TR(8);
 			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
 			f32 const total = __fmul_rn(__fadd_rn(both, sink_e), 255.0f);
 			f32 const w_sink = __fmul_rn(sink_e, 255.0f);
@@ -513,6 +617,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		}
 	}
 
+#ifdef X17_EXPERIMENT_TIMING
+	{
+		bool const sel = blockIdx.x == 20 && blockIdx.y == 3 && blockIdx.z == 0;
+		u32 const role = warp == 0 ? 0u : warp == 1 ? 1u : warp == 2 ? 2u : warp == 6 ? 3u : 9u;
+		if (sel && role < 4 && lane == 0) {
+			// each role's counter lives in the registers of its recording lane
+			g_ntimes[role] = t_n;
+			for (u32 i = 0; i < t_n; ++i) g_times[role][i] = t_buf[role * 128 + i];
+		}
+	}
+#endif
 	tc_fence_before();
 	__syncthreads();
 	if (warp == 1) {

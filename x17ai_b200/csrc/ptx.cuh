@@ -96,6 +96,26 @@ X17_DEV f32 tanh_approx(f32 x) {
 	return r;
 }
 
+// packed f32x2 arithmetic (two IEEE f32 operations per issue slot on sm_100)
+X17_DEV u64 pack_f32x2(f32 lo, f32 hi) {
+	u64 r;
+	asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+	return r;
+}
+X17_DEV void unpack_f32x2(u64 v, f32 &lo, f32 &hi) {
+	asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+X17_DEV u64 fma_f32x2(u64 a, u64 b, u64 c) {
+	u64 d;
+	asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+	return d;
+}
+X17_DEV u64 add_f32x2(u64 a, u64 b) {
+	u64 d;
+	asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+	return d;
+}
+
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 
@@ -150,6 +170,10 @@ X17_DEV bool mbar_wait(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 de
 // warp has arrived on the matching "empty" barrier). All lanes return the same value, so the
 // warp stays converged for the .sync.aligned tcgen05 instructions that follow.
 X17_DEV bool mbar_wait_warp(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 detail) {
+	// fast path: every lane observes the phase itself (one suspended try each, no polling loop)
+	bool mine = mbar_try_wait(bar, parity);
+	if (__all_sync(0xffffffffu, mine)) return true;
+	// slow path: lane 0 runs the bounded wait and broadcasts the verdict
 	u32 ok = 0;
 	if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctx, code, detail) ? 1u : 0u;
 	ok = __shfl_sync(0xffffffffu, ok, 0);
