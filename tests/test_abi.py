@@ -47,7 +47,7 @@ def test_struct_layouts_match_reference():
 def test_meta_matches_launch_contract(lib):
     from x17ai_b200 import kernels as K
     a = K.AttnKernel(K.AttnKernelConfig(32, 128, 4096, 8192, 4096))
-    assert a.THREADS_PER_BLOCK == 192 and a.Q_PER_BLOCK == 128
+    assert a.THREADS_PER_BLOCK == 320 and a.Q_PER_BLOCK == 128
     assert a.Q_PER_BLOCK & (a.Q_PER_BLOCK - 1) == 0          # attn.rs:336-339
     g = K.GemmKernel(K.ffn_f_fwd_config(4096, 14336))
     assert (g.M_PER_BLOCK, g.N_PER_BLOCK) == (128, 256)      # powers of two, gemm.rs:563-566
