@@ -218,6 +218,30 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8(
 	uint32_t const *kv_lens, int8_t const *sink_k, int8_t const *sink_v,
 	float const *attn_temperature, int8_t *out, float *l, size_t window_size, size_t n_splits);
 
+/*
+ * The same decode attention for callers that must not allocate: no counterpart in the
+ * reference. Some hosts of this library run where device memory cannot be allocated at call
+ * time: inside a serving loop whose memory was carved up front and handed out by the host's own
+ * allocator, under a CUDA memory pool that is exhausted or disabled, or in a process whose
+ * policy forbids cudaMalloc / cudaMallocAsync after start-up. For them the split-KV partials
+ * go to a 4 MiB array built into the library image (every GPU that loads the library holds it
+ * until the process exits) instead of stream-ordered scratch.
+ *   - Arguments and results are those of x17ai_b200_attn_decode_i8.
+ *   - Limit: batch * n_heads * n_splits * (head_dim + 2) <= 1,048,576 floats; larger requests are
+ *     rejected with a diagnostic (pass a smaller n_splits, or use the allocating entry point).
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress
+ *     with that device current); make that first call before any stream capture.
+ *   - All calls share the one array: two calls whose kernels may overlap on the GPU (different
+ *     streams, or different threads) race on it. Calls on one stream are safe: each call
+ *     overwrites every slot it later reads, so nothing has to be cleared between calls.
+ *   - It calls no cudaMalloc, cudaFree, cudaMallocAsync or other allocating routine.
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8_noalloc(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
+	int8_t const *q, int8_t const *kv_cache, size_t kv_capacity, size_t kv_len,
+	uint32_t const *kv_lens, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, size_t n_splits);
+
 /* Epilogues of the GEMM (src/device/cuda/gemm.rs: ScaleEpilogue :60-110, RMSNormEpilogue
  * :112-166, ResidualEpilogue :168-212, GeGluEpilogue :214-255) */
 enum {

@@ -92,6 +92,8 @@ SIGNATURES = {
                                      + [c_size_t] + [c_void_p] * 3),
     "x17ai_b200_attn_decode_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_void_p, c_void_p, c_size_t,
                                          c_size_t] + [c_void_p] * 6 + [c_size_t, c_size_t]),
+    "x17ai_b200_attn_decode_i8_noalloc": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_void_p, c_void_p, c_size_t,
+                                                 c_size_t] + [c_void_p] * 6 + [c_size_t, c_size_t]),
     "x17ai_b200_gemm_meta": (DIAG, [POINTER(GemmConfig), POINTER(GemmMeta)]),
     "x17ai_b200_gemm_fwd": (DIAG, [c_void_p, POINTER(GemmConfig), c_void_p, c_size_t, c_void_p, c_size_t,
                                    c_void_p, c_void_p, c_void_p]),

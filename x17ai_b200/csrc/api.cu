@@ -365,6 +365,20 @@ __global__ void split_i8_weights_kernel(int8_t const *w, uint64_t rows, uint64_t
 
 
 
+// ---- decode without allocation -------------------------------------------------------------------
+// Scratch for the split-KV partials of x17ai_b200_attn_decode_i8_noalloc. It lives in the
+// library image: every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t NOALLOC_SCRATCH_FLOATS = size_t(1) << 20;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+struct NoAllocDevice {
+	std::once_flag once;
+	float *scratch = nullptr;  // device address of g_noalloc_scratch on this device
+	int sm_count = 0;
+	cudaError_t err = cudaSuccess;
+};
+NoAllocDevice g_noalloc_dev[MAX_DEVICES];
+
 // fixed-capacity FfiBuffer for x17ai_b200_take_diagnostic
 struct FixedBuf {
 	char *ptr;
@@ -542,6 +556,113 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8(
 		if (res == nullptr) g_launches.fetch_add(1, std::memory_order_relaxed);
 		cudaFreeAsync(p.scratch, s);
 	}
+	return res;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8_noalloc(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
+	int8_t const *q, int8_t const *kv_cache, size_t kv_capacity, size_t kv_len,
+	uint32_t const *kv_lens, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, size_t n_splits) {
+	char const *who = "x17ai_b200_attn_decode_i8_noalloc()";
+	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (batch == 0) return make_diag("x17ai_b200: empty decode input", who, ": decode input q has zero size");
+	if (batch > 65535 || kv_capacity >= (size_t(1) << 31) || kv_len > kv_capacity) {
+		return make_diag("x17ai_b200: decode shape out of range", who, ": decode shape out of range (kv_len ",
+						 kv_len, ", kv_capacity ", kv_capacity, ")");
+	}
+	if (window_size > 0 && window_size % 16 != 0) {
+		return make_diag("x17ai_b200: bad window", who,
+						 ": attention window_size must be zero or divisible by 16, got ", window_size);
+	}
+	if (!q || !kv_cache || !sink_k || !sink_v || !attn_temperature || !out) {
+		return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	}
+	if (!aligned16(q) || !aligned16(kv_cache) || !aligned16(sink_k)) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	if (stream == nullptr) return make_diag("x17ai_b200: null stream", who, ": null stream");
+	if (!x17::driver().ok) {
+		return make_diag("x17ai_b200: CUDA driver not available", who,
+						 ": the CUDA driver is not available on this machine; this library has no CPU path");
+	}
+	// Enter the stream's context by hand: the usual per-device set-up of this library allocates
+	// its status words with cudaMalloc, which this entry point must not do.
+	CUcontext ctx = nullptr;
+	CUresult ce = DRV(cuStreamGetCtx)(reinterpret_cast<CUstream>(stream), &ctx);
+	if (ce == CUDA_SUCCESS) ce = DRV(cuCtxPushCurrent)(ctx);
+	if (ce != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cannot enter the stream's context", who,
+						 ": cannot enter the stream's context: ", x17::cu_error_text(ce));
+	}
+	struct Pop {
+		~Pop() {
+			CUcontext popped = nullptr;
+			DRV(cuCtxPopCurrent)(&popped);
+		}
+	} pop;
+	CUdevice dev = -1;
+	if (DRV(cuCtxGetDevice)(&dev) != CUDA_SUCCESS || int(dev) < 0 || int(dev) >= MAX_DEVICES) {
+		return make_diag("x17ai_b200: cannot resolve the device", who, ": cannot resolve the device");
+	}
+	NoAllocDevice &nd = g_noalloc_dev[int(dev)];
+	// First call on this device (with the device current): resolve the device address of the
+	// scratch array. In host code the array's name is only a stand-in, not a device pointer.
+	std::call_once(nd.once, [&] {
+		nd.err = cudaGetSymbolAddress(reinterpret_cast<void **>(&nd.scratch), g_noalloc_scratch);
+		if (nd.err == cudaSuccess) nd.err = cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, int(dev));
+	});
+	if (nd.err != cudaSuccess || nd.scratch == nullptr) {
+		return make_diag("x17ai_b200: scratch set-up failed", who, ": cudaGetSymbolAddress failed: ",
+						 cudaGetErrorString(nd.err));
+	}
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+	size_t const pairs = batch * cfg->n_heads;
+	if (n_splits == 0) {
+		size_t const want = size_t(nd.sm_count) * 8;
+		n_splits = pairs >= want ? 1 : (want + pairs - 1) / pairs;
+		size_t const max_splits = kv_len / 256 > 0 ? kv_len / 256 : 1;
+		if (n_splits > max_splits) n_splits = max_splits;
+	}
+	uint32_t const d = uint32_t(cfg->head_dim);
+	size_t const need = n_splits > 1 ? pairs * n_splits * (d + 2) : 0;
+	if (n_splits > 65535 || need > NOALLOC_SCRATCH_FLOATS) {
+		return make_diag("x17ai_b200: scratch too small", who, ": batch * n_heads * n_splits * (head_dim + 2) = ",
+						 need, " floats exceeds the built-in scratch of ", NOALLOC_SCRATCH_FLOATS,
+						 " floats (4 MiB); use fewer splits or x17ai_b200_attn_decode_i8");
+	}
+	x17::DecodeParams p{};
+	p.q = q;
+	p.q_stride = cfg->q_stride;
+	p.kv = kv_cache;
+	p.kv_stride = cfg->kv_stride;
+	p.kv_batch_stride = cfg->kv_stride * kv_capacity;
+	p.kv_lens = kv_lens;
+	p.kv_len = uint32_t(kv_len);
+	p.window = window_size == 0 ? 0xFFFFFFFFu : uint32_t(((window_size - 1) / 16 + 1) * 16);
+	p.sink_k = sink_k;
+	p.sink_v = sink_v;
+	p.temperature = attn_temperature;
+	p.out = out;
+	p.o_stride = cfg->o_stride;
+	p.l = l;
+	p.n_heads = uint32_t(cfg->n_heads);
+	p.n_splits = uint32_t(n_splits);
+	p.scratch = nd.scratch;  // every split writes its whole slot before the merge reads it
+	dim3 grid(unsigned(cfg->n_heads), unsigned(batch), unsigned(n_splits));
+	dim3 mgrid(unsigned(cfg->n_heads), unsigned(batch));
+	if (d == 128) {
+		x17::attn_decode_kernel<128><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>(p);
+	} else if (d == 64) {
+		x17::attn_decode_kernel<64><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>(p);
+	} else {
+		x17::attn_decode_kernel<32><<<grid, x17::dec_cfg::THREADS, 0, s>>>(p);
+		if (n_splits > 1) x17::attn_decode_merge_kernel<32><<<mgrid, 32, 0, s>>>(p);
+	}
+	x17ai_DiagnosticBuffer *res = launch_result(who);
+	if (res == nullptr && n_splits > 1) g_launches.fetch_add(1, std::memory_order_relaxed);
 	return res;
 }
 

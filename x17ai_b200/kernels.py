@@ -141,8 +141,10 @@ class AttnKernel:
             _ptr(attn_temperature), _ptr(out), _ptr(l), window_size, _ptr(dbg_s), _ptr(dbg_p), _ptr(dbg_o)))
 
     def decode(self, stream, q, kv_cache, kv_len, sink_k, sink_v, attn_temperature, out, l=None, window_size=0,
-               kv_lens=None, n_splits=0):
-        """One new token per sequence: q [B, q_stride], kv_cache [B, T, kv_stride], out [B, o_stride]."""
+               kv_lens=None, n_splits=0, no_alloc=False):
+        """One new token per sequence: q [B, q_stride], kv_cache [B, T, kv_stride], out [B, o_stride].
+        `no_alloc=True` takes the entry point that keeps its split-KV partials in the library's built-in
+        4 MiB scratch instead of allocating (see x17ai_b200_attn_decode_i8_noalloc in the header)."""
         c = self.config
         batch, _ = matrix_shape("decode", "q", q, (None, c.q_stride), DTYPE_INT8)
         if kv_cache.dim() != 3 or kv_cache.shape[0] != batch or kv_cache.shape[2] != c.kv_stride:
@@ -155,7 +157,8 @@ class AttnKernel:
         if l is not None:
             matrix_shape("decode", "l", l, (batch, c.n_heads), DTYPE_F32)
         cfg = c._c()
-        check(self._lib.x17ai_b200_attn_decode_i8(
+        entry = self._lib.x17ai_b200_attn_decode_i8_noalloc if no_alloc else self._lib.x17ai_b200_attn_decode_i8
+        check(entry(
             stream.handle, ctypes.byref(cfg), batch, _ptr(q), _ptr(kv_cache), kv_cache.shape[1], kv_len,
             _ptr(kv_lens), _ptr(sink_k), _ptr(sink_v), _ptr(attn_temperature), _ptr(out), _ptr(l), window_size,
             n_splits))
