@@ -48,7 +48,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -71,7 +71,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken between the wall-clock times t_begin and t_end (all if None)."""
+        import datetime
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -81,19 +83,35 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        power = []
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0])); mx.append(float(parts[1]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if t_begin is not None and not (t_begin - 0.05 <= ts <= t_end + 0.05):
+                    continue
+                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[3:7]):
+            for n, v in zip(names, parts[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_traffic(workload, units):
+    """DRAM bytes per launch from the committed ncu summary (profiles/traffic.json): bytes per unit of a
+    captured smaller case of the same kernel, scaled to this launch by the units it processes."""
+    p = ROOT / "profiles" / "traffic.json"
+    if not p.exists():
+        return None
+    d = json.loads(p.read_text()).get(workload)
+    if not d:
+        return None
+    return d["dram_bytes_per_unit"] * units
 
 
 def dist_env():
@@ -134,6 +152,7 @@ class AttnPrefill:
         self.ops = o_attn.attn_ops(B, H, D, S, W)
         self.ref_ops = self.kern.config.n_ops(S, W) * B
         self.tokens = B * S
+        self.units = B * H  # (sequence, head) units of this S, D, W
         self.alg_bytes = self.q.numel() + self.kv.numel() + self.out.numel() + self.l.numel() * 4
         self.launches_per_step = 1
         self.config = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H,
@@ -203,6 +222,7 @@ class Ffn:
         self.M, self.Dm, self.F = M, Dm, F
         self.ops = 2.0 * M * Dm * 2 * F + 2.0 * M * F * 2 * Dm
         self.tokens = M
+        self.units = M  # token rows
         self.alg_bytes = M * Dm + 2 * F * Dm + M * F * 2 + 2 * Dm * F + M * Dm * 2
         self.launches_per_step = 2
         self.config = {"workload": "configs[3] gated FFN (GeGLU -> e4m3, gated residual)", "tokens": M, "d_model": Dm,
@@ -267,6 +287,7 @@ class Decode:
         self.kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
         self.ops = 4.0 * B * H * D * (T + 1)
         self.tokens = B
+        self.units = B * H
         self.alg_bytes = self.kv.numel() + self.q.numel() + self.out.numel()
         self.launches_per_step = 1
         self.config = {"workload": "configs[4] decode: int8 attention of one new token per sequence", "batch": B,
@@ -323,6 +344,7 @@ class RmsNorm:
         self.y = torch.empty(M, Dm, dtype=torch.int8, device=device)
         self.ops = 3.0 * M * Dm
         self.tokens = M
+        self.units = M
         self.alg_bytes = 2 * M * Dm
         self.launches_per_step = 1
         self.config = {"workload": "RMSNorm e4m3 -> FixedI8", "rows": M, "cols": Dm,
@@ -402,7 +424,7 @@ def run_reference(args, rank, world):
     else:
         cfg = {"workload": "RMSNorm e4m3 -> FixedI8", "rows": 131072, "cols": 4096}
         unit, metric = "GB/s", "RMSNorm bandwidth"
-    per_step = max(3.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    per_step = max(0.3, min(20.0, 120.0 / max(1, args.steps + args.warmup)))  # the whole run: about two minutes
     vals = []
     sample = ""
     for i in range(args.warmup + args.steps):
@@ -422,8 +444,8 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -460,10 +482,12 @@ def main():
     timers = [device.CudaTimer(stream) for _ in range(args.steps)]
     for _ in range(args.warmup):
         w.step()
-    barrier()
     sampler = ClockSampler(local)
     sampler.start()
+    time.sleep(0.5)  # nvidia-smi needs a moment before its first sample
+    barrier()
     launches0 = lib.x17ai_b200_launch_count()
+    wall0 = time.time()
     t0 = time.perf_counter()
     for i in range(args.steps):
         timers[i].start()
@@ -471,8 +495,10 @@ def main():
         timers[i].stop()
     stream.synchronize()
     t1 = time.perf_counter()
+    wall1 = time.time()
     launches = lib.x17ai_b200_launch_count() - launches0
-    clocks = sampler.stop()
+    time.sleep(0.15)
+    clocks = sampler.stop(wall0, wall1)
     dev_times = [t.elapsed_seconds() for t in timers]
     status = stream.read_status()
     if status != [0, 0, 0, 0]:
@@ -532,7 +558,7 @@ def main():
         "config": dict(w.config, sharding=f"{world} x per-GPU workload, (batch, head) / token-row units, no collective"),
         "tokens_per_s": world * w.tokens * args.steps / dev_total,
         "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_note, "kernel_ms": kernel_avg * 1e3,
+                     "traffic": measured_traffic(args.workload, w.units), "peak_source": peak_note, "kernel_ms": kernel_avg * 1e3,
                      "nominal_frac": achieved / (4500.0 if w.bound == "tensor" else 7700.0)},
         "clocks": clocks,
         "gpu_launches": int(launches),
