@@ -450,6 +450,8 @@ def main():
     ap.add_argument("--workload", default="attn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="N > 1: also time an NCCL all_gather of the step's output "
+                    "(reported separately as gather_ms; the path itself needs no collective)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
                     "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm")
     args = ap.parse_args()
@@ -531,6 +533,23 @@ def main():
         e2e = {"h2d_bytes_per_step": int(w.h2d), "d2h_bytes_per_step": int(w.d2h), "ms_per_step": e2e_time * 1e3,
                "steps": n_e2e}
 
+    gather_ms = None
+    if args.gather and world > 1:
+        out_t = getattr(w, "out", None) if hasattr(w, "out") else getattr(w, "y", None)
+        parts = [torch.empty_like(out_t) for _ in range(world)]
+        for _ in range(2):
+            dist.all_gather(parts, out_t)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(5):
+            dist.all_gather(parts, out_t)
+        ev1.record()
+        torch.cuda.synchronize()
+        g = torch.tensor([ev0.elapsed_time(ev1) / 5], dtype=torch.float64, device=dev)
+        dist.all_reduce(g, op=dist.ReduceOp.MAX)
+        gather_ms = float(g[0])
+
     peaks = measured_peaks()
     if w.bound == "tensor":
         unit, scale = "TOPS", 1e12
@@ -564,6 +583,8 @@ def main():
         "gpu_launches": int(launches),
         "wall_ms_per_step": wall_total / args.steps * 1e3,
     }
+    if gather_ms is not None:
+        line["gather_ms"] = gather_ms
     if args.workload == "attn":
         line["reference_count_tops"] = world * w.ref_ops * args.steps / dev_total / 1e12
     if e2e is not None:
