@@ -192,6 +192,21 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8(
 	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
 	float const *attn_temperature, int8_t *out, float *l, size_t window_size);
 
+/*
+ * The same attention with P.V on the fp8 tensor path and bf16 output.  The reference file of this name
+ * (attn_y_fwd_fp8.cu:11-47) is a bf16 GEMM of the attention output projection; the kernel described for
+ * the benchmark - softmax probabilities quantised to e4m3, V in e4m3 with a per-head f32 scale - has no
+ * counterpart in the reference.  Q.K^T, masks, sink, temperature, maximum and normaliser are those of
+ * x17ai_b200_attn_fwd_i8; P = e4m3(256 * 2^(s - max)) (OCP e4m3, round to nearest even), O accumulates in
+ * f32, out = bf16(O / sum * v_scale[h]), L = log2(256 * sum) + max.
+ *   kv: K half int8 FixedI8 as before, V half OCP e4m3 bytes; sink_v [n_heads][D] e4m3 (same scale);
+ *   v_scale f32 [n_heads]; out bf16 [batch][seq_len][o_stride] (o_stride in elements).
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, uint8_t const *kv, int8_t const *sink_k, uint8_t const *sink_v,
+	float const *attn_temperature, float const *v_scale, uint16_t *out_bf16, float *l, size_t window_size);
+
 /* Same launch with validation outputs: dbg_s int32 [batch*n_heads][seq][seq] raw scores of the
  * visited tiles, dbg_p uint8 [batch*n_heads][seq][seq] quantised probabilities, dbg_o int32
  * [batch*n_heads][seq][D] the int32 P.V accumulator.  Small shapes only. */
@@ -290,6 +305,28 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
 	void const *a, size_t a_rows, void const *b, size_t b_rows,
 	void *c, float *rrms, int8_t const *residual);
+
+/* Fused Q / KV / gate projection of one token block: one GEMM over the row-concatenated weights
+ * [W_q (H*D rows) ; W_kv (H*2*D rows, per head K then V) ; W_g (gate_cols rows)], each column
+ * segment with its own epilogue, so x is read once.  Replaces the two launches attn_q_fwd and
+ * attn_kv_fwd of the reference (src/main.rs:387-491; the stale single-kernel form is
+ * cuda/qkvg_fwd_i8.cuh:145-219): q = fixedi8(acc * inp * out) (ScaledMatrixWriter), k/v and k_rrms as
+ * the RMS_NORM epilogue (L2NormMatrixWriter), g = fixedi8(acc * inp * out) raw gate columns. */
+typedef struct x17ai_QkvgConfig {
+	size_t model_dim; /* K */
+	size_t n_heads;
+	size_t head_dim;  /* 32, 64 or 128; n_heads * head_dim a multiple of 256 */
+	size_t gate_cols; /* 0 = no gate segment; else a multiple of 128 */
+	double inp_scale; /* main.rs:412-421: model_dim^-1/2 / 64 */
+	double out_scale; /* 8 */
+	double eps;       /* 2^-70 */
+} x17ai_QkvgConfig;
+
+/* x [rows][model_dim]; w_qkvg [H*D + 2*H*D + gate_cols][model_dim]; q [rows][H*D]; kv [rows][2*H*D];
+ * k_rrms f32 [rows][H]; g [rows][gate_cols] or NULL when gate_cols is 0. */
+x17ai_DiagnosticBuffer *x17ai_b200_qkvg_fwd_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_QkvgConfig const *cfg, int8_t const *x, size_t rows,
+	int8_t const *w_qkvg, int8_t *q, int8_t *kv, float *k_rrms, int8_t *g);
 
 /* One-time weight preparation for e4m3 activations x int8 weights: writes
  * out[rows][2*cols] e4m3 = [16*hi | lo] with w = 16*hi + lo, hi in [-8, 8], lo in [0, 15],

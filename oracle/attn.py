@@ -188,3 +188,45 @@ def attended_keys_total(seq_len, window):
 def attn_ops(batch, n_heads, head_dim, seq_len, window):
     """Algorithmic operation count of one attention pass: 4 * B*H*D * sum_i (min(i,W')+1)."""
     return 4.0 * batch * n_heads * head_dim * attended_keys_total(seq_len, window)
+
+
+def attn_fwd_pv_fp8(q, k, v_e4m3, sink_k, sink_v_e4m3, temperature, v_scale, window, n_heads, head_dim):
+    """fp8 P.V variant described for the benchmark (no counterpart in the reference; its
+    attn_y_fwd_fp8.cu:11-47 is a bf16 GEMM).  Scores, masks, sink, temperature and maximum as in
+    attn_head (cuda/attn_fwd_i8.cuh:408-450, 489-517); then P = e4m3(256 * 2^(s - max)) with the OCP
+    e4m3 encoding (round to nearest even), V = e4m3 * v_scale[h], O accumulated in float (float64 here,
+    f32 on the tensor core), out = O / sum * v_scale with the un-rounded sum, L = log2(256 * sum) + max.
+    q, k: int8 [S, H*D]; v_e4m3: uint8 [S, H*D]; returns out f32 [S, H*D] (before the bf16 cast), l [H, S]."""
+    from . import formats
+    q = np.asarray(q, dtype=np.int8)
+    k = np.asarray(k, dtype=np.int8)
+    s_len, d = q.shape[0], head_dim
+    w = _round_window(window)
+    out = np.empty((s_len, n_heads * d), dtype=F32)
+    l = np.empty((n_heads, s_len), dtype=F32)
+    i = np.arange(s_len)[:, None]
+    j = np.arange(s_len)[None, :]
+    mask = j >= i
+    if w is not None:
+        mask |= j < i - w
+    for h in range(n_heads):
+        sl = slice(h * d, (h + 1) * d)
+        qf, kf = q[:, sl].astype(F32), k[:, sl].astype(F32)
+        vf = formats.hw_e4m3_to_f32(v_e4m3[:, sl]).astype(np.float64)
+        svf = formats.hw_e4m3_to_f32(sink_v_e4m3[h]).astype(np.float64)
+        temp = (row_temperature(s_len, d, window) * F32(temperature[h])).astype(F32)
+        sink_s = ((qf @ np.asarray(sink_k[h], dtype=np.int8).astype(F32)) * temp).astype(F32)
+        acc = qf @ kf.T
+        # the kernel evaluates fma(acc, temp, -max) with one rounding
+        s64 = acc.astype(np.float64) * temp.astype(np.float64)[:, None]
+        s32 = np.where(mask, -np.inf, (acc * temp[:, None]).astype(F32))
+        m = np.maximum(sink_s, s32.max(axis=1)).astype(F32)
+        x = np.where(mask, -np.inf, (s64 - m.astype(np.float64)[:, None])).astype(F32)
+        p = np.exp2(x).astype(F32)
+        sink_e = np.exp2((sink_s - m).astype(F32)).astype(F32)
+        total = ((p.sum(axis=1, dtype=np.float64) + sink_e).astype(F32) * F32(256.0)).astype(F32)
+        p8 = formats.hw_e4m3_to_f32(formats.hw_f32_to_e4m3((p * F32(256.0)).astype(F32))).astype(np.float64)
+        o = p8 @ vf + (sink_e.astype(np.float64) * 256.0)[:, None] * svf[None, :]
+        out[:, sl] = (o / total.astype(np.float64)[:, None] * float(v_scale[h])).astype(F32)
+        l[h] = (np.log2(total) + m).astype(F32)
+    return out, l

@@ -18,6 +18,7 @@ def pytest_collection_modifyitems(config, items):
     # the shared library is built once for the whole session (cross-compiles without a GPU)
     from x17ai_b200 import build
     build.build()
+    build.build_kernel_objects()
 
 
 @pytest.fixture(scope="session")

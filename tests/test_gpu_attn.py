@@ -164,3 +164,34 @@ def test_attention_argument_errors(stream):
         kern.launch(stream, z(128, 128), z(64, 256), z(2, 64), z(2, 64), z(2, dt=torch.float32), z(128, 128), None, 0)
     with pytest.raises(X17Error, match="has dtype"):
         kern.launch(stream, z(128, 128), z(128, 256), z(2, 64), z(2, 64), z(2, dt=torch.float16), z(128, 128), None, 0)
+
+
+@pytest.mark.parametrize("B,H,D,S,W", [(1, 2, 128, 384, 128), (2, 2, 64, 256, 0), (1, 4, 32, 200, 48)])
+def test_attention_pv_fp8(stream, B, H, D, S, W):
+    """fp8 P.V variant: bf16 output within max-abs error 1e-2 x RMS of the oracle's output (the bar the
+    benchmark description sets for bf16 outputs); parity for this mode is pinned by the oracle only."""
+    from x17ai_b200 import kernels as K
+    rng = np.random.default_rng(B + H + D + S + W)
+    q, kv, sk, _, temp = _inputs(rng, B, S, H, D)
+    v_scale = np.abs(rng.standard_normal(H)).astype(np.float32) + 0.25
+    kv4 = kv.reshape(B, S, H, 2, D).copy()
+    v_val = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    v8 = formats.hw_f32_to_e4m3(v_val)
+    kv4[:, :, :, 1, :] = v8.view(np.int8)
+    kv = kv4.reshape(B, S, 2 * H * D)
+    sv8 = formats.hw_f32_to_e4m3(rng.standard_normal((H, D)).astype(np.float32))
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    tq, tkv, tsk, tsv, tt, tvs = t(q), t(kv), t(sk), t(sv8), t(temp), t(v_scale)
+    out = torch.zeros((B, S, H * D), dtype=torch.bfloat16, device="cuda")
+    l = torch.zeros((B, H, S), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    kern.launch_pv_fp8(stream, tq, tkv, tsk, tsv, tt, tvs, out, l, W)
+    stream.synchronize()
+    got = out.float().cpu().numpy()
+    for b in range(B):
+        k_i8 = kv4[b, :, :, 0, :].reshape(S, H * D)
+        ref, ref_l = o_attn.attn_fwd_pv_fp8(q[b], k_i8, v8[b].reshape(S, H * D), sk, sv8, temp, v_scale, W, H, D)
+        rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+        assert np.max(np.abs(got[b] - ref)) <= 1e-2 * rms + 2.0 ** -8 * np.abs(ref).max()   # + one bf16 ulp of the largest value
+        assert np.max(np.abs(l[b].cpu().numpy() - ref_l)) <= 1e-3

@@ -175,6 +175,33 @@ def test_block_gemms_against_reference_fixtures(stream, name):
     assert (y.cpu().numpy() != g["ffn_y_f8"].reshape(S, Dm)).mean() <= 2e-3
 
 
+@pytest.mark.parametrize("d,heads,gate", [(128, 2, 256), (64, 4, 0), (32, 8, 128)])
+def test_fused_qkvg_projection(stream, d, heads, gate):
+    """One launch equals the reference's two launches (attn_q_fwd, attn_kv_fwd) plus the raw gate columns."""
+    from x17ai_b200 import kernels as K
+    rng = np.random.default_rng(d + heads + gate)
+    m, k = 300, 512
+    hd = heads * d
+    x = _rand_i8(rng, (m, k))
+    wq, wkv, wg = _rand_i8(rng, (hd, k)), _rand_i8(rng, (2 * hd, k)), _rand_i8(rng, (gate, k))
+    w = np.concatenate((wq, wkv, wg), axis=0)
+    tx, tw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    q = torch.zeros((m, hd), dtype=torch.int8, device="cuda")
+    kv = torch.zeros((m, 2 * hd), dtype=torch.int8, device="cuda")
+    rr = torch.zeros((m, heads), dtype=torch.float32, device="cuda")
+    g = torch.zeros((m, gate), dtype=torch.int8, device="cuda") if gate else None
+    torch.cuda.synchronize()
+    K.qkvg_fwd_i8(stream, tx, tw, heads, d, q, kv, rr, g)
+    stream.synchronize()
+    assert np.array_equal(q.cpu().numpy(), o_gemm.attn_q_fwd(x, wq))
+    ref_kv, ref_rr = o_gemm.attn_kv_fwd(x, wkv, d)
+    dd = np.abs(kv.cpu().numpy().astype(np.int32) - ref_kv.astype(np.int32))
+    assert dd.max() <= 1 and (dd > 0).mean() <= 1e-4
+    assert np.max(np.abs(rr.cpu().numpy() - ref_rr) / ref_rr) < 1e-6
+    if gate:
+        assert np.array_equal(g.cpu().numpy(), o_gemm.attn_q_fwd(x, wg))
+
+
 def test_gemm_argument_errors(stream):
     from x17ai_b200 import X17Error, kernels as K
     with pytest.raises(X17Error, match="multiple of 128"):

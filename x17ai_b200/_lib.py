@@ -56,6 +56,11 @@ class GemmConfig(Structure):
                 ("eps", c_double), ("head_dim", c_size_t)]
 
 
+class QkvgConfig(Structure):
+    _fields_ = [("model_dim", c_size_t), ("n_heads", c_size_t), ("head_dim", c_size_t), ("gate_cols", c_size_t),
+                ("inp_scale", c_double), ("out_scale", c_double), ("eps", c_double)]
+
+
 class GemmMeta(Structure):
     _fields_ = [("threads_per_block", c_size_t), ("smem_bytes", c_size_t), ("m_per_block", c_size_t),
                 ("n_per_block", c_size_t)]
@@ -88,6 +93,7 @@ SIGNATURES = {
     "x17ai_cuda_launch_kernel": (DIAG, [c_void_p, c_void_p] + [c_size_t] * 7 + [POINTER(c_void_p)]),
     "x17ai_b200_attn_meta": (DIAG, [POINTER(AttnConfig), POINTER(AttnMeta)]),
     "x17ai_b200_attn_fwd_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7 + [c_size_t]),
+    "x17ai_b200_attn_fwd_pv_fp8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 8 + [c_size_t]),
     "x17ai_b200_attn_fwd_i8_debug": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7
                                      + [c_size_t] + [c_void_p] * 3),
     "x17ai_b200_attn_decode_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_void_p, c_void_p, c_size_t,
@@ -97,6 +103,7 @@ SIGNATURES = {
     "x17ai_b200_gemm_meta": (DIAG, [POINTER(GemmConfig), POINTER(GemmMeta)]),
     "x17ai_b200_gemm_fwd": (DIAG, [c_void_p, POINTER(GemmConfig), c_void_p, c_size_t, c_void_p, c_size_t,
                                    c_void_p, c_void_p, c_void_p]),
+    "x17ai_b200_qkvg_fwd_i8": (DIAG, [c_void_p, POINTER(QkvgConfig), c_void_p, c_size_t] + [c_void_p] * 5),
     "x17ai_b200_split_i8_weights": (DIAG, [c_void_p, c_void_p, c_size_t, c_size_t, c_void_p]),
     "x17ai_b200_rms_norm": (DIAG, [c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_double]),
     "x17ai_b200_read_status": (DIAG, [c_void_p, POINTER(c_uint32)]),

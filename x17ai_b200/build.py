@@ -45,5 +45,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_kernel_objects():
+    """The cubin + meta.json kernel objects used by the tests (prebuilt so they travel with the tree)."""
+    from . import kernel_objects
+    for dim in (512, 4096):
+        kernel_objects.build_rms_norm(dim)
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose=True)

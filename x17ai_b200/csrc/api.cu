@@ -179,12 +179,12 @@ uint32_t rounded_window(size_t window_size, size_t seq_len) {
 	return w >= seq_len ? 0xFFFFFFFFu : uint32_t(w);
 }
 
-template <bool DEBUG>
+template <bool DEBUG, bool FP8PV = false>
 x17ai_DiagnosticBuffer *attn_launch(
 	char const *who, x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
 	size_t seq_len, int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
-	float const *temperature, int8_t *out, float *l, size_t window_size, int32_t *dbg_s,
-	uint8_t *dbg_p, int32_t *dbg_o) {
+	float const *temperature, void *out, float *l, size_t window_size, int32_t *dbg_s,
+	uint8_t *dbg_p, int32_t *dbg_o, float const *v_scale = nullptr) {
 	if (auto *d = check_attn_config(cfg, who)) return d;
 	if (batch == 0 || seq_len == 0) {
 		return make_diag("x17ai_b200: empty attention input", who, ": attention input q has zero size");
@@ -232,6 +232,7 @@ x17ai_DiagnosticBuffer *attn_launch(
 	p.o_batch_stride = cfg->o_stride * seq_len;
 	p.l = l;
 	p.l_batch_stride = cfg->n_heads * seq_len;
+	p.v_scale = v_scale;
 	p.status = scope.state().status;
 	p.dbg_s = dbg_s;
 	p.dbg_p = dbg_p;
@@ -250,11 +251,11 @@ x17ai_DiagnosticBuffer *attn_launch(
 	};
 	cudaError_t ce;
 	if (d == 128) {
-		ce = go(x17::attn_fwd_kernel<128, DEBUG>, x17::attn_cfg::smem_bytes<128>());
+		ce = go(x17::attn_fwd_kernel<128, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<128>());
 	} else if (d == 64) {
-		ce = go(x17::attn_fwd_kernel<64, DEBUG>, x17::attn_cfg::smem_bytes<64>());
+		ce = go(x17::attn_fwd_kernel<64, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<64>());
 	} else {
-		ce = go(x17::attn_fwd_kernel<32, DEBUG>, x17::attn_cfg::smem_bytes<32>());
+		ce = go(x17::attn_fwd_kernel<32, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<32>());
 	}
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
@@ -465,6 +466,17 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8(
 	float const *attn_temperature, int8_t *out, float *l, size_t window_size) {
 	return attn_launch<false>("x17ai_b200_attn_fwd_i8()", stream, cfg, batch, seq_len, q, kv, sink_k, sink_v,
 							  attn_temperature, out, l, window_size, nullptr, nullptr, nullptr);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, uint8_t const *kv, int8_t const *sink_k, uint8_t const *sink_v,
+	float const *attn_temperature, float const *v_scale, uint16_t *out_bf16, float *l, size_t window_size) {
+	if (v_scale == nullptr) return static_diag("x17ai_b200_attn_fwd_pv_fp8(): null v_scale");
+	return attn_launch<false, true>("x17ai_b200_attn_fwd_pv_fp8()", stream, cfg, batch, seq_len, q,
+									reinterpret_cast<int8_t const *>(kv), sink_k,
+									reinterpret_cast<int8_t const *>(sink_v), attn_temperature, out_bf16, l,
+									window_size, nullptr, nullptr, nullptr, v_scale);
 }
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_debug(
@@ -774,6 +786,76 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	case x17::EPI_RESID_E4M3: ce = gemm_go<x17::EPI_RESID_E4M3>(plan.f8, grid, s, ta, tb, p); break;
 	default: ce = gemm_go<x17::EPI_RESID_I8>(plan.f8, grid, s, ta, tb, p); break;
 	}
+	if (ce != cudaSuccess) {
+		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
+						 cudaGetErrorString(ce));
+	}
+	return launch_result(who);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_qkvg_fwd_i8(
+	x17ai_CudaStreamHandle *stream, x17ai_QkvgConfig const *cfg, int8_t const *x, size_t rows,
+	int8_t const *w_qkvg, int8_t *q, int8_t *kv, float *k_rrms, int8_t *g) {
+	char const *who = "x17ai_b200_qkvg_fwd_i8()";
+	if (cfg == nullptr) return make_diag("x17ai_b200: null config", who, ": null config");
+	size_t const hd = cfg->n_heads * cfg->head_dim;
+	size_t const n_q = hd, n_kv = 2 * hd, n_g = cfg->gate_cols;
+	if (cfg->n_heads == 0 || (cfg->head_dim != 32 && cfg->head_dim != 64 && cfg->head_dim != 128)) {
+		return make_diag("x17ai_b200: bad qkvg config", who, ": qkvg requires n_heads > 0 and head_dim 32, 64 or 128");
+	}
+	if (cfg->model_dim == 0 || cfg->model_dim % 128 != 0) {
+		return make_diag("x17ai_b200: bad qkvg config", who, ": qkvg requires model_dim to be a non-zero multiple of 128, got ",
+						 cfg->model_dim);
+	}
+	if (n_q % x17::gemm_cfg::BN != 0 || n_g % 128 != 0) {
+		return make_diag("x17ai_b200: bad qkvg config", who, ": qkvg requires n_heads * head_dim to be a multiple of ",
+						 x17::gemm_cfg::BN, " and gate_cols a multiple of 128, got ", n_q, " and ", n_g);
+	}
+	if (rows == 0) return make_diag("x17ai_b200: empty input", who, ": qkvg input x has zero size");
+	if (rows >= (size_t(1) << 31)) return make_diag("x17ai_b200: shape out of range", who, ": too many rows");
+	if (!x || !w_qkvg || !q || !kv || !k_rrms || (n_g != 0 && !g)) {
+		return make_diag("x17ai_b200: null tensor", who, ": null tensor argument");
+	}
+	if (!aligned16(x) || !aligned16(w_qkvg) || !aligned16(q) || !aligned16(kv) || (g && !aligned16(g))) {
+		return make_diag("x17ai_b200: misaligned tensor", who, ": tensors must be 16-byte aligned");
+	}
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	using namespace x17::gemm_cfg;
+	size_t const n_raw = n_q + n_kv + n_g;
+	CUtensorMap ta, tb;
+	CUresult e = make_map_2d(&ta, x, cfg->model_dim, rows, cfg->model_dim, BK, BM);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, w_qkvg, cfg->model_dim, n_raw, cfg->model_dim, BK, BN);
+	if (e != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
+						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
+	}
+	x17::GemmParams p{};
+	p.m = uint32_t(rows);
+	p.n_raw = uint32_t(n_raw);
+	p.k = p.k_a = uint32_t(cfg->model_dim);
+	p.tiles_m = uint32_t((rows + BM - 1) / BM);
+	p.tiles_n = uint32_t((n_raw + BN - 1) / BN);
+	p.c = q;
+	p.c_stride = n_q;
+	p.c2 = kv;
+	p.c2_stride = n_kv;
+	p.c3 = g;
+	p.c3_stride = n_g;
+	p.n_q = uint32_t(n_q);
+	p.n_kv = uint32_t(n_kv);
+	p.rrms = k_rrms;
+	p.rrms_cols = uint32_t(cfg->n_heads);
+	p.head_dim = uint32_t(cfg->head_dim);
+	p.status = scope.state().status;
+	p.k0 = float(cfg->eps);
+	p.k1 = float(cfg->out_scale * std::sqrt(double(cfg->head_dim)));
+	p.k2 = float(cfg->inp_scale * cfg->out_scale);
+	p.k3 = float(cfg->inp_scale * cfg->out_scale);
+	p.k4 = float(cfg->inp_scale * cfg->out_scale);
+	uint32_t const n_tiles = p.tiles_m * p.tiles_n;
+	uint32_t const ctas = n_tiles < uint32_t(scope.state().sm_count) ? n_tiles : uint32_t(scope.state().sm_count);
+	cudaError_t ce = gemm_go<x17::EPI_QKVG>(false, dim3(ctas), reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
 						 cudaGetErrorString(ce));

@@ -39,8 +39,9 @@ struct AttnParams {
 	i8 const *sink_k;
 	i8 const *sink_v;
 	f32 const *temperature;
-	i8 *out;
-	u64 o_stride, o_batch_stride;
+	void *out;  // int8 FixedI8, or bf16 in the fp8 P.V mode
+	u64 o_stride, o_batch_stride;  // in elements of the output type
+	f32 const *v_scale;  // fp8 P.V mode: per-head scale of the e4m3 V values
 	f32 *l;  // [batch][head][seq] or null
 	u64 l_batch_stride;
 	u32 *status;
@@ -112,10 +113,12 @@ X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u3
 
 // Same arithmetic, same roundings, with the four f32 operations per element issued as packed
 // f32x2 instructions (two elements per issue slot).
-template <bool EDGE>
+// FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
+template <bool EDGE, bool FP8 = false>
 X17_DEV void softmax_chunk_v2(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
 							  f32 (&sum)[4], u32 (&pk)[8]) {
 	using namespace attn_cfg;
+	u64 const s256 = pack_f32x2(256.0f, 256.0f);
 	u64 const neg_magic2 = pack_f32x2(-MAGIC, -MAGIC);
 	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
 	u64 const temp2 = pack_f32x2(temp, temp);
@@ -142,16 +145,26 @@ X17_DEV void softmax_chunk_v2(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m,
 			u64 const e2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
 			if (h == 0) sum01 = add_f32x2(sum01, e2);
 			else sum23 = add_f32x2(sum23, e2);
-			// rint(255 * ex) lands in the low mantissa byte
-			u64 const q2 = fma_f32x2(e2, s255, magic2);
-			f32 qa, qb;
-			unpack_f32x2(q2, qa, qb);
-			q4[2 * h] = __float_as_uint(qa);
-			q4[2 * h + 1] = __float_as_uint(qb);
+			if constexpr (FP8) {
+				f32 qa, qb;
+				unpack_f32x2(mul_f32x2(e2, s256), qa, qb);
+				q4[h] = cvt_e4m3x2(qa, qb);
+			} else {
+				// rint(255 * ex) lands in the low mantissa byte
+				u64 const q2 = fma_f32x2(e2, s255, magic2);
+				f32 qa, qb;
+				unpack_f32x2(q2, qa, qb);
+				q4[2 * h] = __float_as_uint(qa);
+				q4[2 * h + 1] = __float_as_uint(qb);
+			}
 		}
-		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
-		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
-		pk[g] = __byte_perm(lo2, hi2, 0x5410);
+		if constexpr (FP8) {
+			pk[g] = q4[0] | (q4[1] << 16);
+		} else {
+			u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
+			u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
+			pk[g] = __byte_perm(lo2, hi2, 0x5410);
+		}
 	}
 	unpack_f32x2(sum01, sum[0], sum[1]);
 	unpack_f32x2(sum23, sum[2], sum[3]);
@@ -186,7 +199,9 @@ __device__ unsigned g_ntimes[4];
 #define X17_T(role, tag) do {} while (0)
 #endif
 
-template <u32 D, bool DEBUG>
+// FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
+// accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
+template <u32 D, bool DEBUG, bool FP8PV = false>
 __global__ void __launch_bounds__(attn_cfg::THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
 				const AttnParams p) {
@@ -296,7 +311,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		// ---------------- MMA issuer ----------------
 		if (elect_one()) {
 			constexpr u32 idesc_qk = make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, BQ, BKV);
-			constexpr u32 idesc_pv = make_idesc(DFMT_S32, FMT_U8, FMT_S8, 0, 1, BQ, D);
+			constexpr u32 idesc_pv = FP8PV ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 1, BQ, D)
+										   : make_idesc(DFMT_S32, FMT_U8, FMT_S8, 0, 1, BQ, D);
 			u32 const o_tmem = tmem_base + O_COL;
 			bool ok = mbar_wait(q_full_bar, 0, ctx, ST_WAIT_Q_FULL, 0);
 			u32 it = 0;
@@ -337,8 +353,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				for (u32 ks = 0; ks < BKV / 32; ++ks) {
 					// A: +32 bytes along the key axis inside the swizzle row;
 					// B (MN-major): +32 key rows of D bytes each
-					mma_i8_ss(o_tmem, p_desc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
-							  (!first || ks != 0) ? 1u : 0u);
+					if constexpr (FP8PV) {
+						mma_f8_ss(o_tmem, p_desc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
+								  (!first || ks != 0) ? 1u : 0u);
+					} else {
+						mma_i8_ss(o_tmem, p_desc + 2 * ks, bdesc + ((32 * D) >> 4) * ks, idesc_pv,
+								  (!first || ks != 0) ? 1u : 0u);
+					}
 				}
 				X17_T(1, 6);
 				tc_commit(empty_bar(s));
@@ -531,11 +552,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			X17_TR(4);
 			u32 pk0[8], pk1[8];
 			if (edge) {
-				softmax_chunk_v2<true>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk_v2<true>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk_v2<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk_v2<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			} else {
-				softmax_chunk_v2<false>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk_v2<false>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk_v2<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk_v2<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
 			X17_TR(5);
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
@@ -575,13 +596,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			tc_fence_after();
 			X17_TR(8);
 			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
-			f32 const total = __fmul_rn(__fadd_rn(both, sink_e), 255.0f);
-			f32 const w_sink = __fmul_rn(sink_e, 255.0f);
+			constexpr f32 PS = FP8PV ? 256.0f : 255.0f;  // scale of the quantised probabilities
+			f32 const total = __fmul_rn(__fadd_rn(both, sink_e), PS);
+			f32 const w_sink = __fmul_rn(sink_e, PS);
 			f32 const recip = rcp_approx(total);
 			constexpr u32 HALF_D = D / 2;
 			u32 const d0 = half * HALF_D;
-			i8 *const out_row =
-				p.out + u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D + d0;
+			u64 const out_off = u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D + d0;
+			f32 const vs = FP8PV ? __ldg(p.v_scale + head) : 1.0f;
 #pragma unroll
 			for (u32 c = 0; c < HALF_D; c += 16) {
 				u32 r[16];
@@ -589,24 +611,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				tmem_wait_ld();
 				uint4 const sv = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + d0 + c));
 				u32 const svw[4] = {sv.x, sv.y, sv.z, sv.w};
-				u32 pk[4];
+				if constexpr (FP8PV) {
+					// O is f32 = sum of (256 p) * e4m3(v); sink_v is e4m3 too; out = bf16(value * v_scale)
+					f32 o[16];
 #pragma unroll
-				for (u32 g = 0; g < 4; ++g) {
-					u32 b4[4];
-#pragma unroll
-					for (u32 e = 0; e < 4; ++e) {
-						f32 const svf = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
-						f32 const o = __fmaf_rn(w_sink, svf, __int2float_rn(i32(r[4 * g + e])));
-						b4[e] = u32(f32_to_fixedi8(__fmul_rn(o, recip)));
+					for (u32 i = 0; i < 16; ++i) {
+						f32 const svf = hw_e4m3_to_f32(svw[i >> 2] >> (8 * (i & 3)));
+						o[i] = __fmul_rn(__fmul_rn(__fmaf_rn(w_sink, svf, __uint_as_float(r[i])), recip), vs);
 					}
-					pk[g] = pack4(b4[0], b4[1], b4[2], b4[3]);
-				}
-				if (row_ok) {
-					*reinterpret_cast<uint4 *>(out_row + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-					if constexpr (DEBUG) {
-						i32 *d = p.dbg_o + ((u64(batch) * p.n_heads + head) * p.seq_len + qi) * D + d0 + c;
+					if (row_ok) {
+						uint4 *dst = reinterpret_cast<uint4 *>(static_cast<u16 *>(p.out) + out_off + c);
+						dst[0] = make_uint4(cvt_bf16x2(o[0], o[1]), cvt_bf16x2(o[2], o[3]), cvt_bf16x2(o[4], o[5]),
+											cvt_bf16x2(o[6], o[7]));
+						dst[1] = make_uint4(cvt_bf16x2(o[8], o[9]), cvt_bf16x2(o[10], o[11]), cvt_bf16x2(o[12], o[13]),
+											cvt_bf16x2(o[14], o[15]));
+					}
+				} else {
+					u32 pk[4];
 #pragma unroll
-						for (u32 i = 0; i < 16; ++i) d[i] = i32(r[i]);
+					for (u32 g = 0; g < 4; ++g) {
+						u32 b4[4];
+#pragma unroll
+						for (u32 e = 0; e < 4; ++e) {
+							f32 const svf = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
+							f32 const o = __fmaf_rn(w_sink, svf, __int2float_rn(i32(r[4 * g + e])));
+							b4[e] = u32(f32_to_fixedi8(__fmul_rn(o, recip)));
+						}
+						pk[g] = pack4(b4[0], b4[1], b4[2], b4[3]);
+					}
+					if (row_ok) {
+						*reinterpret_cast<uint4 *>(static_cast<i8 *>(p.out) + out_off + c) =
+							make_uint4(pk[0], pk[1], pk[2], pk[3]);
+						if constexpr (DEBUG) {
+							i32 *d = p.dbg_o + ((u64(batch) * p.n_heads + head) * p.seq_len + qi) * D + d0 + c;
+#pragma unroll
+							for (u32 i = 0; i < 16; ++i) d[i] = i32(r[i]);
+						}
 					}
 				}
 			}

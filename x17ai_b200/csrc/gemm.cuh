@@ -27,6 +27,7 @@ enum GemmEpilogue : int {
 	EPI_RESID_E4M3 = 3,  // raw (2j, 2j+1) = (gate, value), gated residual -> e4m3
 	EPI_RESID_I8 = 4,    // same -> fixedi8
 	EPI_RAW_I32 = 5,     // raw 32-bit accumulators (validation of the int32 / f32 accumulation)
+	EPI_QKVG = 6,        // fused projection: raw columns [q | kv | g], each segment its own epilogue
 };
 
 struct GemmParams {
@@ -41,6 +42,13 @@ struct GemmParams {
 	u32 rrms_cols;
 	u32 head_dim;
 	f32 k0, k1, k2, k3, k4;  // epilogue constants, see the epilogue functions
+	// EPI_QKVG: raw columns [0, n_q) -> c (q, scale k3); [n_q, n_q + n_kv) -> c2 (kv, L2-norm as
+	// EPI_L2NORM_KV with k0..k2, rrms); the rest -> c3 (g, scale k4). Segments are multiples of BN.
+	u32 n_q, n_kv;
+	void *c2;
+	u64 c2_stride;
+	void *c3;
+	u64 c3_stride;
 	u32 *status;
 };
 
@@ -226,7 +234,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 			bool const row_ok = row < p.m;
 			u32 const t_base = tmem_base + buf * ACC_COLS + ((quarter * 32u) << 16);
 
-			if constexpr (EPI == EPI_L2NORM_KV) {
+			if constexpr (EPI == EPI_QKVG) {
+				if (n0 < p.n_q || n0 >= p.n_q + p.n_kv) {
+					// q or g segment: plain scale -> FixedI8 (ScaledMatrixWriter, gemm_b8.cuh:291-339)
+					bool const is_q = n0 < p.n_q;
+					i8 *const base = static_cast<i8 *>(is_q ? p.c : p.c3);
+					u64 const stride = is_q ? p.c_stride : p.c3_stride;
+					u32 const col0 = is_q ? n0 : n0 - p.n_q - p.n_kv;
+					u32 const width = is_q ? p.n_q : p.n_raw - p.n_q - p.n_kv;
+					f32 const sc = is_q ? p.k3 : p.k4;
+					for (u32 c = 0; c < BN && col0 + c < width; c += 32) {
+						u32 r[32];
+						tmem_ld_32x32b_x32(t_base + c, r);
+						tmem_wait_ld();
+						u32 w[8];
+#pragma unroll
+						for (u32 i = 0; i < 8; ++i) {
+							w[i] = pack4(u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 0]), sc))),
+										 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 1]), sc))),
+										 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 2]), sc))),
+										 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 3]), sc))));
+						}
+						if (row_ok) {
+							uint4 *dst = reinterpret_cast<uint4 *>(base + u64(row) * stride + col0 + c);
+							dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+							dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+						}
+					}
+				} else {
+					// kv segment: per head [K(D) | V(D)] (L2NormMatrixWriter, gemm_b8.cuh:861-949)
+					u32 const d = p.head_dim;
+					u32 const col0 = n0 - p.n_q;
+					for (u32 h0 = 0; h0 < BN && col0 + h0 < p.n_kv; h0 += 2 * d) {
+						f32 ssum = 0.0f;
+						for (u32 c = 0; c < d; c += 32) {
+							u32 r[32];
+							tmem_ld_32x32b_x32(t_base + h0 + c, r);
+							tmem_wait_ld();
+#pragma unroll
+							for (u32 i = 0; i < 32; ++i) {
+								f32 f = acc_to_f32<F8>(r[i]);
+								ssum = __fmaf_rn(f, f, ssum);
+							}
+						}
+						f32 const kscale = __fmul_rn(rsqrt_approx(__fadd_rn(ssum, p.k0)), p.k1);
+						if (row_ok) p.rrms[u64(row) * p.rrms_cols + (col0 + h0) / (2 * d)] = kscale;
+						for (u32 c = 0; c < 2 * d; c += 32) {
+							u32 r[32];
+							tmem_ld_32x32b_x32(t_base + h0 + c, r);
+							tmem_wait_ld();
+							f32 const sc = c < d ? kscale : p.k2;
+							u32 w[8];
+#pragma unroll
+							for (u32 i = 0; i < 8; ++i) {
+								w[i] = pack4(u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 0]), sc))),
+											 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 1]), sc))),
+											 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 2]), sc))),
+											 u32(f32_to_fixedi8(__fmul_rn(acc_to_f32<F8>(r[4 * i + 3]), sc))));
+							}
+							if (row_ok) {
+								uint4 *dst = reinterpret_cast<uint4 *>(
+									static_cast<i8 *>(p.c2) + u64(row) * p.c2_stride + col0 + h0 + c);
+								dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+								dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+							}
+						}
+					}
+				}
+			} else if constexpr (EPI == EPI_L2NORM_KV) {
 				// raw columns of a head: [K(D) | V(D)]; the tile holds BN / 2D whole heads.
 				// k0 = eps, k1 = HEAD_SCALE (= out_scale * sqrt(D)), k2 = SEP_SCALE (= inp * out)
 				u32 const d = p.head_dim;

@@ -110,6 +110,23 @@ X17_DEV u64 fma_f32x2(u64 a, u64 b, u64 c) {
 	asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
 	return d;
 }
+X17_DEV u64 mul_f32x2(u64 a, u64 b) {
+	u64 d;
+	asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+	return d;
+}
+// two f32 -> two OCP e4m3 bytes (round to nearest even, saturating): lo in bits 0-7, hi in 8-15
+X17_DEV u32 cvt_e4m3x2(f32 lo, f32 hi) {
+	unsigned short r;
+	asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+	return r;
+}
+// two f32 -> two bf16 (round to nearest even): lo in bits 0-15, hi in 16-31
+X17_DEV u32 cvt_bf16x2(f32 lo, f32 hi) {
+	u32 r;
+	asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+	return r;
+}
 X17_DEV u64 add_f32x2(u64 a, u64 b) {
 	u64 d;
 	asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
@@ -355,6 +372,15 @@ X17_DEV f32 e4m3_to_f32(u32 code) {
 	u32 rest = (code & 0x7Fu) << 4;
 	u32 bf = ((sign | rest) + (120u << 7)) & 0xFFFFu;
 	return rest == 0 ? 0.0f : __uint_as_float(bf << 16);
+}
+
+// one OCP e4m3 byte (subnormals included) -> f32 through the hardware converter
+X17_DEV f32 hw_e4m3_to_f32(u32 code) {
+	u32 h2;
+	asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(h2) : "r"(code & 0xFFu));
+	f32 r;
+	asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.f32.f16 %0, lo;\n\t}" : "=f"(r) : "r"(h2));
+	return r;
 }
 
 X17_DEV u32 pack4(u32 b0, u32 b1, u32 b2, u32 b3) {

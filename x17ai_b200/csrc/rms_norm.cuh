@@ -71,8 +71,7 @@ X17_DEV f32 bf16_lo(u32 w) { return __uint_as_float(w << 16); }
 X17_DEV f32 bf16_hi(u32 w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 template <int MODE>
-__global__ void __launch_bounds__(rms_cfg::THREADS)
-rms_norm_kernel(const RmsParams p) {
+X17_DEV void rms_norm_body(RmsParams const &p) {
 	using namespace rms_cfg;
 	constexpr u32 VALS = MODE == RMS_E4M3_FIXED ? 16 : 8;  // values per 16-byte chunk
 	u32 const warp = threadIdx.x >> 5;
@@ -174,6 +173,12 @@ rms_norm_kernel(const RmsParams p) {
 			}
 		}
 	}
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(rms_cfg::THREADS)
+rms_norm_kernel(const RmsParams p) {
+	rms_norm_body<MODE>(p);
 }
 
 }  // namespace x17

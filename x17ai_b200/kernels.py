@@ -133,6 +133,23 @@ class AttnKernel:
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
             _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
 
+    def launch_pv_fp8(self, stream, q, kv, sink_k, sink_v, attn_temperature, v_scale, out, l=None, window_size=0):
+        """fp8 P.V variant: kv holds int8 K and e4m3 V bytes (int8 view), sink_v e4m3, out bf16."""
+        c = self.config
+        batch = q.shape[0] if q.dim() == 3 else 1
+        q2, kv2, out2 = (q[0], kv[0], out[0]) if q.dim() == 3 else (q, kv, out)
+        seq_len, _ = matrix_shape("attention", "q", q2, (None, c.q_stride), DTYPE_INT8)
+        matrix_shape("attention", "kv", kv2, (seq_len, c.kv_stride), DTYPE_INT8)
+        matrix_shape("attention", "sink_k", sink_k, (c.n_heads, c.head_dim), DTYPE_INT8)
+        matrix_shape("attention", "sink_v", sink_v, (c.n_heads, c.head_dim), DTYPE_E4M3)
+        vector_shape("attention", "attn_temperature", attn_temperature, c.n_heads, DTYPE_F32)
+        vector_shape("attention", "v_scale", v_scale, c.n_heads, DTYPE_F32)
+        matrix_shape("attention", "out", out2, (seq_len, c.o_stride), DTYPE_BF16)
+        cfg = c._c()
+        check(self._lib.x17ai_b200_attn_fwd_pv_fp8(
+            stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
+            _ptr(attn_temperature), _ptr(v_scale), _ptr(out), _ptr(l), window_size))
+
     def launch_debug(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, dbg_s, dbg_p, dbg_o):
         batch, seq_len = self._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
         cfg = self.config._c()
@@ -222,6 +239,22 @@ class GemmKernel:
         cfg = g._c()
         check(self._lib.x17ai_b200_gemm_fwd(stream.handle, ctypes.byref(cfg), _ptr(a), a_rows, _ptr(b), g.b_rows,
                                             _ptr(c), _ptr(rrms), _ptr(residual)))
+
+
+def qkvg_fwd_i8(stream, x, w_qkvg, n_heads, head_dim, q, kv, k_rrms, g=None, eps=2.0 ** -70):
+    """Fused Q / KV / gate projection (attn_q_fwd + attn_kv_fwd of src/main.rs:387-491 in one launch)."""
+    rows, model_dim = matrix_shape("qkvg", "x", x, (None, None), DTYPE_INT8)
+    hd = n_heads * head_dim
+    gate_cols = 0 if g is None else g.shape[1]
+    matrix_shape("qkvg", "w_qkvg", w_qkvg, (3 * hd + gate_cols, model_dim), DTYPE_INT8)
+    matrix_shape("qkvg", "q", q, (rows, hd), DTYPE_INT8)
+    matrix_shape("qkvg", "kv", kv, (rows, 2 * hd), DTYPE_INT8)
+    matrix_shape("qkvg", "k_rrms", k_rrms, (rows, n_heads), DTYPE_F32)
+    if g is not None:
+        matrix_shape("qkvg", "g", g, (rows, gate_cols), DTYPE_INT8)
+    cfg = _lib.QkvgConfig(model_dim, n_heads, head_dim, gate_cols, model_dim ** -0.5 / 64.0, FIXED_I8_SCALE, eps)
+    check(_lib.load().x17ai_b200_qkvg_fwd_i8(stream.handle, ctypes.byref(cfg), _ptr(x), rows, _ptr(w_qkvg), _ptr(q),
+                                              _ptr(kv), _ptr(k_rrms), _ptr(g)))
 
 
 def split_i8_weights(stream, w):
