@@ -114,9 +114,9 @@ X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u3
 // Same arithmetic, same roundings, with the four f32 operations per element issued as packed
 // f32x2 instructions (two elements per issue slot).
 // FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
-template <bool EDGE, bool FP8 = false>
-X17_DEV void softmax_chunk_v2(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
-							  f32 (&sum)[4], u32 (&pk)[8]) {
+template <bool EDGE, bool FP8 = false, u32 N = 32>
+X17_DEV void softmax_chunk_v2(u32 const (&r)[N], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
+							  f32 (&sum)[4], u32 (&pk)[N / 4]) {
 	using namespace attn_cfg;
 	u64 const s256 = pack_f32x2(256.0f, 256.0f);
 	u64 const neg_magic2 = pack_f32x2(-MAGIC, -MAGIC);
@@ -127,7 +127,7 @@ X17_DEV void softmax_chunk_v2(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m,
 	u64 sum01 = pack_f32x2(sum[0], sum[1]);
 	u64 sum23 = pack_f32x2(sum[2], sum[3]);
 #pragma unroll
-	for (u32 g = 0; g < 8; ++g) {
+	for (u32 g = 0; g < N / 4; ++g) {
 		u32 q4[4];
 #pragma unroll
 		for (u32 h = 0; h < 2; ++h) {
@@ -300,8 +300,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			};
 			// sweep 1: K tiles. sweep 2, in the order the MMA warp consumes them:
 			// K[first], then K[t+1] before V[t] (Q.K^T of the next tile is issued ahead of P.V)
+			#pragma unroll 1
 			for (u32 t = t_begin; t <= t_end && ok; ++t) ok = load(t, 0);
 			if (ok) ok = load(t_begin, 0);
+			#pragma unroll 1
 			for (u32 t = t_begin; t <= t_end && ok; ++t) {
 				if (t < t_end) ok = load(t + 1, 0);
 				if (ok) ok = load(t, 1);
@@ -379,6 +381,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			};
 
 			// sweep 1: the scores ping-pong between the two halves of the allocation
+			#pragma unroll 1
 			for (u32 t = t_begin; t <= t_end && ok; ++t) {
 				u32 const b = (t - t_begin) & 1u;
 				ok = wait_s_read(b, t) && issue_qk(b);
@@ -387,6 +390,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			// once, so Q.K^T of tile t+1 runs while they work on tile t
 			if (ok) ok = wait_s_read(0, t_begin) && issue_qk(0);
 			u32 n_p = 0;
+			#pragma unroll 1
 			for (u32 t = t_begin; t <= t_end && ok; ++t) {
 				if (t < t_end) ok = wait_s_read(0, t) && issue_qk(0);
 				if (!ok) break;
@@ -460,6 +464,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		i32 ext[4];
 #pragma unroll
 		for (u32 i = 0; i < 4; ++i) ext[i] = pos_t ? INT32_MIN : INT32_MAX;
+		#pragma unroll 1
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			u32 const b = (t - t_begin) & 1u;
 			u32 const par = b == 0 ? (use0 & 1u) : (use1 & 1u);
@@ -530,6 +535,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		u32 const p_row = s_p + row * 128u;
 		u32 const sw = row & 7u;
 		u32 const ch0 = half * 4u;  // first of this thread's four 16-byte chunks
+		#pragma unroll 1
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			if (!mbar_wait_warp(s_full_bar(0), use0 & 1, ctx, ST_WAIT_S_FULL, t)) {
 				ok = false;
@@ -542,6 +548,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
 			if (edge) visible(k0, lo, span);
+#ifdef X17_EXPERIMENT_SMALL_LOOP
+			u32 const ta = tmem_base + lane_addr + col_base;
+			if (t > t_begin) {
+				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
+					ok = false;
+					break;
+				}
+			}
+#pragma unroll 1
+			for (u32 c = 0; c < 64; c += 16) {
+				u32 r[16];
+				tmem_ld_32x32b_x16(ta + c, r);
+				tmem_wait_ld();
+				u32 pk[4];
+				if (edge) {
+					softmax_chunk_v2<true, FP8PV, 16>(r, col_base + c, temp, neg_m, lo, span, sum, pk);
+				} else {
+					softmax_chunk_v2<false, FP8PV, 16>(r, col_base + c, temp, neg_m, lo, span, sum, pk);
+				}
+				st_shared_v4(p_row + (((ch0 + (c >> 4)) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+			}
+			tc_fence_before();
+			mbar_arrive(s_done_bar(0));
+#else
 			u32 r0[32], r1[32];
 			u32 const ta = tmem_base + lane_addr + col_base;
 			tmem_ld_32x32b_x32(ta, r0);
@@ -569,9 +599,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			st_shared_v4(p_row + (((ch0 + 1) ^ sw) << 4), pk0[4], pk0[5], pk0[6], pk0[7]);
 			st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
 			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
+#endif
 			fence_proxy_async_smem();
 			mbar_arrive(p_ready_bar);
 			X17_TR(6);
+#ifndef X17_EXPERIMENT_SMALL_LOOP
 			if constexpr (DEBUG) {
 				if (row_ok) {
 					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
@@ -583,6 +615,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 					}
 				}
 			}
+#endif
 		}
 
 		// ---- normalise and store: each thread of the pair takes half of the D columns ----

@@ -169,17 +169,27 @@ X17_DEV bool mbar_try_wait(u32 bar, u32 parity) {
 constexpr u32 WAIT_FAST_POLLS = 1u << 10;
 constexpr u32 WAIT_SLOW_POLLS = 1u << 17;  // x up to 20 us of suspension each: a second or two
 
-X17_DEV bool mbar_wait(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 detail) {
+// The polling loops live in one out-of-line function: inlined and unrolled at every wait they
+// made up most of the kernels' code and thrashed the instruction cache.
+__device__ __noinline__ bool mbar_wait_slow(u32 bar, u32 parity, volatile u32 *abort_flag, u32 *status,
+											u32 code, u32 detail) {
+#pragma unroll 1
 	for (u32 i = 0; i < WAIT_FAST_POLLS; ++i) {
 		if (mbar_try_wait(bar, parity)) return true;
 	}
+#pragma unroll 1
 	for (u32 i = 0; i < WAIT_SLOW_POLLS; ++i) {
 		if (mbar_try_wait(bar, parity)) return true;
-		if (*ctx.abort_flag != 0) return false;
+		if (*abort_flag != 0) return false;
 	}
-	*ctx.abort_flag = 1;
-	report_status(ctx.status, code, detail);
+	*abort_flag = 1;
+	report_status(status, code, detail);
 	return false;
+}
+
+X17_DEV bool mbar_wait(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u32 detail) {
+	if (mbar_try_wait(bar, parity)) return true;
+	return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, code, detail);
 }
 
 // Warp-uniform bounded wait: lane 0 polls, the verdict is broadcast, and on success every lane
@@ -195,6 +205,7 @@ X17_DEV bool mbar_wait_warp(u32 bar, u32 parity, WaitCtx const &ctx, u32 code, u
 	if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctx, code, detail) ? 1u : 0u;
 	ok = __shfl_sync(0xffffffffu, ok, 0);
 	if (ok) {
+#pragma unroll 1
 		for (u32 i = 0; i < WAIT_FAST_POLLS; ++i) {
 			if (mbar_try_wait(bar, parity)) break;
 		}
