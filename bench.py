@@ -405,6 +405,11 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
+    try:  # torchrun pins OMP_NUM_THREADS=1: give the BLAS under numpy every host core back
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
     # build the workload description without touching a GPU
     cls = {"attn": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode, "rms_norm": RmsNorm}[args.workload]
     w = cls.__new__(cls)
