@@ -195,3 +195,30 @@ def test_attention_pv_fp8(stream, B, H, D, S, W):
         rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
         assert np.max(np.abs(got[b] - ref)) <= 1e-2 * rms + 2.0 ** -8 * np.abs(ref).max()   # + one bf16 ulp of the largest value
         assert np.max(np.abs(l[b].cpu().numpy() - ref_l)) <= 1e-3
+
+
+def test_attention_from_host_matches_single_launch(stream):
+    """launch_from_host (per-sequence upload -> kernel -> download over three streams) returns
+    exactly what one batched launch on device-resident data returns."""
+    from x17ai_b200 import device, kernels as K
+    B, H, D, S, W = 5, 2, 64, 300, 64
+    q, kv, sk, sv, temp = _inputs(np.random.default_rng(11), B, S, H, D)
+    want, _ = _launch(stream, q, kv, sk, sv, temp, H, D, W)
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    h_q, h_kv = t(q).pin_memory(), t(kv).pin_memory()
+    h_out = torch.zeros((B, S, H * D), dtype=torch.int8).pin_memory()
+    d_q, d_kv, d_out = torch.zeros_like(h_q, device="cuda"), torch.zeros_like(h_kv, device="cuda"), torch.zeros_like(h_out, device="cuda")
+    tsk, tsv, tt = t(sk).cuda(), t(sv).cuda(), t(temp).cuda()
+    torch.cuda.synchronize()
+    extra = [device.CudaStream(0), device.CudaStream(0)]
+    streams = [stream] + extra
+    for _ in range(2):   # twice: the second round reuses every staging buffer
+        kern.launch_from_host(streams, h_q, h_kv, tsk, tsv, tt, d_q, d_kv, d_out, h_out, None, W)
+    for st in streams:
+        st.synchronize()
+    assert np.array_equal(h_out.numpy(), want)
+    with pytest.raises(Exception, match="pinned"):
+        kern.launch_from_host(streams, t(q), h_kv, tsk, tsv, tt, d_q, d_kv, d_out, h_out, None, W)
+    for st in extra:
+        st.close()

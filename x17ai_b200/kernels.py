@@ -133,6 +133,33 @@ class AttnKernel:
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
             _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
 
+    def launch_from_host(self, streams, h_q, h_kv, sink_k, sink_v, attn_temperature, q, kv, out, h_out,
+                         l=None, window_size=0):
+        """Batched attention whose q, kv arrive from and whose out returns to pinned host memory.
+
+        Sequences are independent, so sequence b goes through streams[b % len(streams)] as
+        upload -> kernel -> download; with two or more streams the copies of one sequence overlap the
+        kernel and the opposite-direction copy of its neighbours. `q`, `kv`, `out` ([B, S, cols]) are
+        the device staging buffers, `h_q`, `h_kv`, `h_out` their pinned host counterparts. Returns
+        after queueing; the caller synchronises every stream before reading `h_out`."""
+        batch, seq_len = self._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
+        if q.dim() != 3:
+            raise X17Error("launch_from_host wants batched [B, S, cols] tensors")
+        for h, d, name in ((h_q, q, "q"), (h_kv, kv, "kv"), (h_out, out, "out")):
+            if tuple(h.shape) != tuple(d.shape) or h.dtype != d.dtype or not h.is_contiguous():
+                raise X17Error(f"host buffer {name} must match its device buffer in shape and dtype")
+            if not h.is_pinned():
+                raise X17Error(f"host buffer {name} must be pinned")
+        cfg = self.config._c()
+        for b in range(batch):
+            st = streams[b % len(streams)]
+            st.upload(h_q[b].data_ptr(), q[b].data_ptr(), 0, q[b].numel())
+            st.upload(h_kv[b].data_ptr(), kv[b].data_ptr(), 0, kv[b].numel())
+            check(self._lib.x17ai_b200_attn_fwd_i8(
+                st.handle, ctypes.byref(cfg), 1, seq_len, _ptr(q[b]), _ptr(kv[b]), _ptr(sink_k), _ptr(sink_v),
+                _ptr(attn_temperature), _ptr(out[b]), _ptr(l[b]) if l is not None else None, window_size))
+            st.download(out[b].data_ptr(), h_out[b].data_ptr(), 0, out[b].numel())
+
     def launch_pv_fp8(self, stream, q, kv, sink_k, sink_v, attn_temperature, v_scale, out, l=None, window_size=0):
         """fp8 P.V variant: kv holds int8 K and e4m3 V bytes (int8 view), sink_v e4m3, out bf16."""
         c = self.config
