@@ -907,7 +907,11 @@ x17ai_DiagnosticBuffer *x17ai_b200_rms_norm(
 	dim3 grid(unsigned((rows + x17::rms_cfg::WARPS - 1) / x17::rms_cfg::WARPS));
 	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 	if (mode == X17AI_RMS_E4M3_FIXED) {
-		x17::rms_norm_kernel<x17::RMS_E4M3_FIXED><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+		if (cols <= size_t(x17::rms_cfg::KEEP_CHUNKS) * 32 * 16) {
+			x17::rms_norm_keep_kernel<<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+		} else {
+			x17::rms_norm_kernel<x17::RMS_E4M3_FIXED><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
+		}
 	} else if (mode == X17AI_RMS_BF16_FIXED) {
 		x17::rms_norm_kernel<x17::RMS_BF16_FIXED><<<grid, x17::rms_cfg::THREADS, 0, s>>>(p);
 	} else {

@@ -25,5 +25,9 @@ kernel(unsigned char const *inp, unsigned long long n_inputs, signed char *out) 
 	p.out_stride = MODEL_DIM;
 	p.eps = float(L2_NORM_EPS);
 	p.inv_cols = float(1.0 / double(MODEL_DIM));
-	x17::rms_norm_body<x17::RMS_E4M3_FIXED>(p);
+	if constexpr (MODEL_DIM <= x17::rms_cfg::KEEP_CHUNKS * 32 * 16) {
+		x17::rms_norm_body_keep(p);
+	} else {
+		x17::rms_norm_body<x17::RMS_E4M3_FIXED>(p);
+	}
 }
