@@ -386,6 +386,79 @@ class RmsNorm:
         return n * 2 * x.size / dt, f"{n} x [4096, 4096] rows, {dt:.1f} s"
 
 
+class Block:
+    """The reference harness's block forward (src/main.rs:193-255): six kernels per step on one batch of
+    sequences at the benchmark's model shape; batch entries go through the block one sequence at a time."""
+    name = "block_fwd"
+    bound = "tensor"
+    dtype = "s8/e4m3"
+
+    def __init__(self, stream, device, B=2, S=8192, Dm=4096, H=32, D=128, F=14336, W=1024, seed=0, fused=True):
+        import torch
+        from x17ai_b200.block import BlockConfig, BlockForward
+        self.torch, self.stream = torch, stream
+        g = torch.Generator(device=device).manual_seed(seed)
+        codes = lambda *s: torch.clamp(torch.round(torch.randn(*s, generator=g, device=device) * 8.0), -127, 127).to(torch.int8)
+        self.x = codes(B, S, Dm)
+        self.blk = BlockForward(stream, BlockConfig(Dm, H, D, F, W), codes(H * D, Dm), codes(2 * H * D, Dm),
+                                codes(2 * Dm, H * D), codes(2 * F, Dm), codes(2 * Dm, F), codes(H, D), codes(H, D),
+                                (0.5 + torch.rand(H, generator=g, device=device)).float(), fused_qkv=fused)
+        self.B, self.S = B, S
+        self.Dm, self.H, self.D, self.F, self.W = Dm, H, D, F, W
+        self.stage_ops = self.blk.n_ops(S)
+        self.ops = B * sum(self.stage_ops.values())
+        self.tokens = B * S
+        self.units = B * S
+        self.alg_bytes = 0
+        self.launches_per_step = B * (5 if fused else 6)
+        self.config = {"workload": "block forward: q/kv projection, int8 attention, attn_y, GeGLU FFN, ffn_y (e4m3 x int8)",
+                       "batch": B, "seq_len": S, "d_model": Dm, "n_heads": H, "head_dim": D, "hidden": F, "window": W,
+                       "fused_qkv": fused, "l2": "weights 0.42 GB + activations per sequence 0.4 GB, larger than the 126 MB L2"}
+        torch.cuda.synchronize()
+
+    def step(self):
+        for b in range(self.B):
+            self.blk.forward(self.x[b])
+
+    def host_buffers(self):
+        t = self.torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_y = t.empty((self.B, self.S, self.Dm), dtype=t.uint8).pin_memory()
+        self.h2d, self.d2h = self.h_x.numel(), self.h_y.numel()
+
+    def e2e_step(self):
+        s = self.stream
+        for b in range(self.B):
+            s.upload(self.h_x[b].data_ptr(), self.x[b].data_ptr(), 0, self.x[b].numel())
+            out = self.blk.forward(self.x[b])
+            s.download(out["ffn_y"].data_ptr(), self.h_y[b].data_ptr(), 0, out["ffn_y"].numel())
+
+    def cpu_sample(self, seconds_hint=15.0):
+        """Oracle on a bounded sample: the six stages on a short sequence of the same model shape."""
+        from oracle import attn as o_attn, gemm as o_gemm
+        Dm, H, D, F, W = self.Dm, self.H, self.D, self.F, self.W
+        S = 256
+        rng = np.random.default_rng(0)
+        mk = lambda *s: np.clip(np.rint(rng.standard_normal(s) * 8), -127, 127).astype(np.int8)
+        x, wq, wkv, way, wf, wy = mk(S, Dm), mk(H * D, Dm), mk(2 * H * D, Dm), mk(2 * Dm, H * D), mk(2 * F, Dm), mk(2 * Dm, F)
+        sk, sv, temp = mk(H, D), mk(H, D), np.ones(H, np.float32)
+        t0, n = time.perf_counter(), 0
+        while True:
+            q = o_gemm.attn_q_fwd(x, wq)
+            kv, _ = o_gemm.attn_kv_fwd(x, wkv, D)
+            ao, _ = o_attn.attn_fwd_i8(q, kv, sk, sv, temp, W, H, D, kv_tile=16)
+            o_gemm.attn_y_fwd(ao, way, x)
+            f = o_gemm.ffn_f_fwd(x, wf)
+            o_gemm.ffn_y_fwd_f8(f, wy, x)
+            n += 1
+            if time.perf_counter() - t0 > seconds_hint:
+                break
+        dt = time.perf_counter() - t0
+        ops = (2.0 * S * Dm * (3 * H * D) + 2.0 * S * H * D * 2 * Dm + 2.0 * S * Dm * 2 * F + 2.0 * S * F * 2 * Dm
+               + o_attn.attn_ops(1, H, D, S, W))
+        return n * ops / dt, f"{n} block forwards of a {S}-token sequence at the same model shape, {dt:.1f} s"
+
+
 def _shape(args, n):
     if not args.shape:
         return None
@@ -401,6 +474,7 @@ WORKLOADS = {
     "ffn_f8": lambda s, d, a=None: Ffn(s, d, True, *(_shape(a, 3) or ())),
     "decode": lambda s, d, a=None: Decode(s, d, *(_shape(a, 5) or ())),
     "rms_norm": lambda s, d, a=None: RmsNorm(s, d, *(_shape(a, 2) or ())),
+    "block": lambda s, d, a=None: Block(s, d, *(_shape(a, 7) or ())),
 }
 
 
@@ -417,7 +491,8 @@ def run_reference(args, rank, world):
     except Exception:
         pass
     # build the workload description without touching a GPU
-    cls = {"attn": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode, "rms_norm": RmsNorm}[args.workload]
+    cls = {"attn": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode, "rms_norm": RmsNorm,
+           "block": Block}[args.workload]
     w = cls.__new__(cls)
     if args.workload == "attn":
         w.S, w.D, w.W, B, H = 8192, 128, 1024, 8, 32
@@ -432,6 +507,11 @@ def run_reference(args, rank, world):
         w.D, w.T, w.W = 128, 4096, 4096
         cfg = {"workload": "configs[4] decode", "batch": 256, "n_heads": 32, "head_dim": 128, "kv_len": 4096}
         unit, metric = "GB/s", "int8 decode attention KV-cache bandwidth"
+    elif args.workload == "block":
+        w.Dm, w.H, w.D, w.F, w.W = 4096, 32, 128, 14336, 1024
+        cfg = {"workload": "block forward: q/kv projection, int8 attention, attn_y, GeGLU FFN, ffn_y (e4m3 x int8)",
+               "batch": 2, "seq_len": 8192, "d_model": 4096, "n_heads": 32, "head_dim": 128, "hidden": 14336, "window": 1024}
+        unit, metric = "TOPS", "quantized block forward throughput"
     else:
         cfg = {"workload": "RMSNorm e4m3 -> FixedI8", "rows": 131072, "cols": 4096}
         unit, metric = "GB/s", "RMSNorm bandwidth"
@@ -464,7 +544,7 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N > 1: also time an NCCL all_gather of the step's output "
                     "(reported separately as gather_ms; the path itself needs no collective)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
-                    "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm")
+                    "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()
@@ -586,7 +666,7 @@ def main():
     line = {
         "metric": {"attn": "int8 sliding-window attention prefill throughput", "ffn_i8": "gated FFN forward throughput",
                    "ffn_f8": "gated FFN forward throughput", "decode": "int8 decode attention KV-cache bandwidth",
-                   "rms_norm": "RMSNorm bandwidth"}[args.workload],
+                   "rms_norm": "RMSNorm bandwidth", "block": "quantized block forward throughput"}[args.workload],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic (seeded N(0,1) values quantised to FixedI8 codes)",

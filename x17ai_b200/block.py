@@ -1,0 +1,132 @@
+"""The reference's block forward as one object: the six launches of src/main.rs:193-255 in its
+order, on buffers allocated once.
+
+  q      = attn_q_fwd(x, W_q)                      FixedI8            (main.rs:195-200)
+  kv     = attn_kv_fwd(x, W_kv)  + k_rrms          FixedI8, K rows L2-normalised per head (:204-209)
+  attn   = attn_fwd_i8(q, kv, sinks, temperature)  FixedI8 + L        (:213-222)
+  attn_y = attn_y_fwd(attn, W_attn_y, residual x)  e4m3               (:226-231)
+  ffn_f  = ffn_f_fwd(x, W_ffn_f)                   e4m3 (GeGLU)       (:235-240)
+  ffn_y  = ffn_y_fwd_f8(ffn_f, W_ffn_y, residual x) e4m3              (:244-249)
+
+Like the reference's harness, both output projections take `x` as the residual and the FFN reads
+`x`: the six kernels are the block's kernels, each fed the tensor the reference feeds it.
+`fused_qkv=True` replaces the first two launches by the single fused projection.
+Every launch goes through the C ABI on the given stream; nothing here computes on the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import kernels as K
+from .device import CudaTimer
+
+
+@dataclass(frozen=True)
+class BlockConfig:
+    """Shape constants of the reference's harness (src/main.rs:30-47)."""
+    model_dim: int
+    n_heads: int
+    head_dim: int
+    ffn_width: int
+    window_size: int
+
+    @property
+    def attn_width(self) -> int:
+        return self.n_heads * self.head_dim
+
+
+class BlockForward:
+    """Weights are int8 device tensors in the reference's layouts ([outputs, inputs], trans = true):
+    w_q [H*D, Dm], w_kv [2*H*D, Dm] (per head K then V), w_attn_y [2*Dm, H*D], w_ffn_f [2*F, Dm],
+    w_ffn_y [2*Dm, F]; sinks [H, D] int8; temperature [H] f32."""
+
+    STAGES = ("attn_q", "attn_kv", "attn", "attn_y", "ffn_f", "ffn_y")
+
+    def __init__(self, stream, config: BlockConfig, w_q, w_kv, w_attn_y, w_ffn_f, w_ffn_y, sink_k, sink_v,
+                 attn_temperature, fused_qkv: bool = False):
+        c = self.config = config
+        self.stream = stream
+        self.fused_qkv = fused_qkv
+        hd = c.attn_width
+        if fused_qkv and hd % 256 != 0:
+            raise K.X17Error(f"fused_qkv needs n_heads * head_dim to be a multiple of 256, got {hd}")
+        self.w_q, self.w_kv, self.w_attn_y, self.w_ffn_f = w_q, w_kv, w_attn_y, w_ffn_f
+        self.sink_k, self.sink_v, self.attn_temperature = sink_k, sink_v, attn_temperature
+        self.k_q = K.GemmKernel(K.attn_q_fwd_config(c.model_dim, hd))
+        self.k_kv = K.GemmKernel(K.attn_kv_fwd_config(c.model_dim, 2 * hd, c.head_dim))
+        self.k_attn = K.AttnKernel(K.AttnKernelConfig(c.n_heads, c.head_dim, hd, 2 * hd, hd))
+        self.k_attn_y = K.GemmKernel(K.attn_y_fwd_config(hd, c.model_dim))
+        self.k_ffn_f = K.GemmKernel(K.ffn_f_fwd_config(c.model_dim, c.ffn_width))
+        self.k_ffn_y = K.GemmKernel(K.ffn_y_fwd_f8_config(c.ffn_width, c.model_dim))
+        # e4m3 activations x int8 weights run on the fp8 tensor path with the weights split once
+        self.w_ffn_y_split = K.split_i8_weights(stream, w_ffn_y)
+        if fused_qkv:
+            self.w_qkv = torch.cat((w_q, w_kv), dim=0).contiguous()
+        stream.synchronize()
+        self._rows = 0
+        self._timers = None
+
+    def _buffers(self, rows: int, device):
+        if rows == self._rows:
+            return
+        c, hd = self.config, self.config.attn_width
+        e = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=device)
+        self.q = e(rows, hd, dtype=torch.int8)
+        self.kv = e(rows, 2 * hd, dtype=torch.int8)
+        self.k_rrms = e(rows, c.n_heads, dtype=torch.float32)
+        self.attn_out = e(rows, hd, dtype=torch.int8)
+        self.attn_l = e(c.n_heads, rows, dtype=torch.float32)
+        self.attn_y = e(rows, c.model_dim, dtype=torch.uint8)
+        self.ffn_f = e(rows, c.ffn_width, dtype=torch.uint8)
+        self.ffn_y = e(rows, c.model_dim, dtype=torch.uint8)
+        torch.cuda.synchronize(device)
+        self._rows = rows
+
+    def n_ops(self, rows: int) -> dict:
+        """Operation counts per stage in the reference's conventions (gemm.rs:445-449, attn.rs:449-471)."""
+        c = self.config
+        return {
+            "attn_q": self.k_q.config.n_ops(rows),
+            "attn_kv": self.k_kv.config.n_ops(rows),
+            "attn": self.k_attn.config.n_ops(rows, c.window_size),
+            "attn_y": self.k_attn_y.config.n_ops(rows),
+            "ffn_f": self.k_ffn_f.config.n_ops(rows),
+            "ffn_y": self.k_ffn_y.config.n_ops(rows),
+        }
+
+    def forward(self, x, timed: bool = False) -> dict:
+        """One sequence `x` [rows, model_dim] int8 (FixedI8 codes) through the six kernels. Returns the
+        device tensors by the reference's names; with `timed`, `self.seconds` holds per-stage device
+        times after the call (the call then synchronises, like the harness)."""
+        c, s = self.config, self.stream
+        rows, _ = K.matrix_shape("block", "x", x, (None, c.model_dim), K.DTYPE_INT8)
+        self._buffers(rows, x.device)
+        if timed and self._timers is None:
+            self._timers = {name: CudaTimer(s) for name in self.STAGES}
+        t = self._timers if timed else None
+
+        def stage(name, fn):
+            if t is not None:
+                t[name].start()
+            fn()
+            if t is not None:
+                t[name].stop()
+
+        if self.fused_qkv:
+            stage("attn_q", lambda: K.qkvg_fwd_i8(s, x, self.w_qkv, c.n_heads, c.head_dim, self.q, self.kv, self.k_rrms))
+            stage("attn_kv", lambda: None)
+        else:
+            stage("attn_q", lambda: self.k_q.launch(s, x, self.w_q, self.q))
+            stage("attn_kv", lambda: self.k_kv.launch(s, x, self.w_kv, self.kv, rrms=self.k_rrms))
+        stage("attn", lambda: self.k_attn.launch(s, self.q, self.kv, self.sink_k, self.sink_v, self.attn_temperature,
+                                                 self.attn_out, self.attn_l, c.window_size))
+        stage("attn_y", lambda: self.k_attn_y.launch(s, self.attn_out, self.w_attn_y, self.attn_y, residual=x))
+        stage("ffn_f", lambda: self.k_ffn_f.launch(s, x, self.w_ffn_f, self.ffn_f))
+        stage("ffn_y", lambda: self.k_ffn_y.launch(s, self.ffn_f, self.w_ffn_y_split, self.ffn_y, residual=x))
+        if t is not None:
+            s.synchronize()
+            self.seconds = {name: t[name].elapsed_seconds() for name in self.STAGES}
+        return {"q": self.q, "kv": self.kv, "k_rrms": self.k_rrms, "attn_out": self.attn_out, "attn_l": self.attn_l,
+                "attn_y": self.attn_y, "ffn_f": self.ffn_f, "ffn_y": self.ffn_y}
