@@ -71,7 +71,9 @@ def run_config(ref: Path, name: str, cfg) -> None:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference project>")
+    ref = Path(sys.argv[1])
     for name, cfg in CONFIGS.items():
         run_config(ref, name, cfg)
 
