@@ -49,18 +49,19 @@ X17_DEV void e4m3x2_to_f32(u32 pair16, f32 &a, f32 &b) {
 		: "r"(h2));
 }
 
-// rint(clamp(v, -127, 127)) of four f32 packed into bytes, without the conversion unit:
-// adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits (round half to even,
-// like cvt.rni), a saturating pack clamps to [-128, 127] and a byte-wise max lifts -128 to -127.
-X17_DEV u32 pack4_fixedi8(f32 v0, f32 v1, f32 v2, f32 v3) {
-	// valid for |v| < 2^22 (here |v| <= 8 * sqrt(cols))
+// rint(clamp(v, -127, 127)) of four values, given as two f32x2 pairs already scaled, packed into
+// bytes without the conversion unit: adding 1.5 * 2^23 leaves the rounded integer in the low
+// mantissa bits (round half to even, like cvt.rni; valid for |v| < 2^22, here |v| <= 8 * sqrt(cols)),
+// a saturating pack clamps to [-128, 127] and a byte-wise max lifts -128 to -127.
+X17_DEV u32 pack4_fixedi8_x2(u64 v01, u64 v23) {
 	constexpr f32 MAGIC = 12582912.0f;
 	constexpr i32 MAGIC_BITS = 0x4B400000;
-	i32 const i0 = __float_as_int(__fadd_rn(v0, MAGIC)) - MAGIC_BITS;
-	i32 const i1 = __float_as_int(__fadd_rn(v1, MAGIC)) - MAGIC_BITS;
-	i32 const i2 = __float_as_int(__fadd_rn(v2, MAGIC)) - MAGIC_BITS;
-	i32 const i3 = __float_as_int(__fadd_rn(v3, MAGIC)) - MAGIC_BITS;
-	// d = sat(a) << 8 | sat(b) | c << 16: build the upper half first, then shift it up
+	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
+	f32 a, b, c, d;
+	unpack_f32x2(add_f32x2(v01, magic2), a, b);
+	unpack_f32x2(add_f32x2(v23, magic2), c, d);
+	i32 const i0 = __float_as_int(a) - MAGIC_BITS, i1 = __float_as_int(b) - MAGIC_BITS;
+	i32 const i2 = __float_as_int(c) - MAGIC_BITS, i3 = __float_as_int(d) - MAGIC_BITS;
 	u32 hi, packed;
 	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(i3), "r"(i2));
 	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed) : "r"(i1), "r"(i0), "r"(hi));
@@ -137,6 +138,7 @@ X17_DEV void rms_norm_body(RmsParams const &p) {
 	}
 	// (x * rrms) * 8 == x * (rrms * 8) exactly: 8 is a power of two
 	f32 const mul8 = MODE == RMS_BF16_ROWSCALE ? mul : __fmul_rn(mul, 8.0f);
+	u64 const mul8_2 = pack_f32x2(mul8, mul8);  // scaling and rounding run as packed f32x2
 
 	if constexpr (MODE == RMS_E4M3_FIXED) {
 		uint4 *dst = reinterpret_cast<uint4 *>(p.out + u64(row) * p.out_stride);
@@ -151,8 +153,7 @@ X17_DEV void rms_norm_body(RmsParams const &p) {
 					f32 x0, x1, x2, x3;
 					e4m3x2_to_f32(wds[i] & 0xFFFFu, x0, x1);
 					e4m3x2_to_f32(wds[i] >> 16, x2, x3);
-					o[i] = pack4_fixedi8(__fmul_rn(x0, mul8), __fmul_rn(x1, mul8), __fmul_rn(x2, mul8),
-										 __fmul_rn(x3, mul8));
+					o[i] = pack4_fixedi8_x2(mul_f32x2(pack_f32x2(x0, x1), mul8_2), mul_f32x2(pack_f32x2(x2, x3), mul8_2));
 				}
 				if (ci < n_chunks) dst[ci] = make_uint4(o[0], o[1], o[2], o[3]);
 			}
@@ -165,10 +166,10 @@ X17_DEV void rms_norm_body(RmsParams const &p) {
 			if (s < per_lane) {
 				u32 const ci = s * 32 + lane;
 				u32 const wds[4] = {regs[s].x, regs[s].y, regs[s].z, regs[s].w};
-				u32 const o0 = pack4_fixedi8(__fmul_rn(bf16_lo(wds[0]), mul8), __fmul_rn(bf16_hi(wds[0]), mul8),
-											 __fmul_rn(bf16_lo(wds[1]), mul8), __fmul_rn(bf16_hi(wds[1]), mul8));
-				u32 const o1 = pack4_fixedi8(__fmul_rn(bf16_lo(wds[2]), mul8), __fmul_rn(bf16_hi(wds[2]), mul8),
-											 __fmul_rn(bf16_lo(wds[3]), mul8), __fmul_rn(bf16_hi(wds[3]), mul8));
+				u32 const o0 = pack4_fixedi8_x2(mul_f32x2(pack_f32x2(bf16_lo(wds[0]), bf16_hi(wds[0])), mul8_2),
+												mul_f32x2(pack_f32x2(bf16_lo(wds[1]), bf16_hi(wds[1])), mul8_2));
+				u32 const o1 = pack4_fixedi8_x2(mul_f32x2(pack_f32x2(bf16_lo(wds[2]), bf16_hi(wds[2])), mul8_2),
+												mul_f32x2(pack_f32x2(bf16_lo(wds[3]), bf16_hi(wds[3])), mul8_2));
 				if (ci < n_chunks) dst[ci] = make_uint2(o0, o1);
 			}
 		}
@@ -193,22 +194,6 @@ X17_DEV void f16x2_to_f32(u32 h2, f32 &a, f32 &b) {
 		: "=f"(a), "=f"(b)
 		: "r"(h2));
 }
-// rint(clamp(v, -127, 127)) of four values given as two f32x2 pairs already scaled
-X17_DEV u32 pack4_fixedi8_x2(u64 v01, u64 v23) {
-	constexpr f32 MAGIC = 12582912.0f;
-	constexpr i32 MAGIC_BITS = 0x4B400000;
-	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
-	f32 a, b, c, d;
-	unpack_f32x2(add_f32x2(v01, magic2), a, b);
-	unpack_f32x2(add_f32x2(v23, magic2), c, d);
-	i32 const i0 = __float_as_int(a) - MAGIC_BITS, i1 = __float_as_int(b) - MAGIC_BITS;
-	i32 const i2 = __float_as_int(c) - MAGIC_BITS, i3 = __float_as_int(d) - MAGIC_BITS;
-	u32 hi, packed;
-	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(i3), "r"(i2));
-	asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed) : "r"(i1), "r"(i0), "r"(hi));
-	return __vmaxs4(packed, 0x81818181u);
-}
-
 X17_DEV void rms_norm_body_keep(RmsParams const &p) {
 	using namespace rms_cfg;
 	u32 const warp = threadIdx.x >> 5;
