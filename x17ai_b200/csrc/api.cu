@@ -420,7 +420,7 @@ size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_
 	return buf.len;
 }
 
-#ifdef X17_EXPERIMENT_TIMING
+#ifdef X17_ATTN_TIMELINE
 // experiment builds only: copies the recorded timeline to the host
 int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
 	cudaDeviceSynchronize();

@@ -63,7 +63,7 @@ constexpr u32 O_COL = 128;
 constexpr u32 XCHG_BYTES = ROW_THREADS * 4;
 template <u32 D>
 constexpr u32 smem_bytes() {
-#ifdef X17_EXPERIMENT_TIMING
+#ifdef X17_ATTN_TIMELINE
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256 + 4096;
 #else
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
@@ -78,44 +78,13 @@ X17_DEV void st_shared_v4(u32 addr, u32 a, u32 b, u32 c, u32 d) {
 				 : "memory");
 }
 
-// 32 score columns of one row -> probabilities: accumulates the un-rounded exp2 into sum[4] and
+// N score columns of one row -> probabilities: accumulates the un-rounded exp2 into sum[4] and
 // returns rint(255 * p) packed four to a word. EDGE: only columns lo <= col < lo + span are visible.
-template <bool EDGE>
-X17_DEV void softmax_chunk(u32 const (&r)[32], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
-						   f32 (&sum)[4], u32 (&pk)[8]) {
-	using namespace attn_cfg;
-#pragma unroll
-	for (u32 g = 0; g < 8; ++g) {
-		u32 q4[4];
-#pragma unroll
-		for (u32 e = 0; e < 4; ++e) {
-			u32 const i = 4 * g + e;
-			// exact int -> float without the conversion unit (|acc| < 2^22)
-			f32 const f = __fsub_rn(__uint_as_float(r[i] + MAGIC_BITS), MAGIC);
-			f32 x = __fmaf_rn(f, temp, neg_m);
-			if constexpr (EDGE) {
-				x = (col0 + i - lo) < span ? x : -INFINITY;
-			}
-#ifdef X17_EXPERIMENT_NO_EX2
-			f32 const ex = x * 1e-9f + 0.5f;
-#else
-			f32 const ex = ex2_approx(x);
-#endif
-			sum[e] = __fadd_rn(sum[e], ex);
-			// rint(255 * ex) lands in the low mantissa byte
-			q4[e] = __float_as_uint(__fmaf_rn(ex, 255.0f, MAGIC));
-		}
-		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
-		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
-		pk[g] = __byte_perm(lo2, hi2, 0x5410);
-	}
-}
-
-// Same arithmetic, same roundings, with the four f32 operations per element issued as packed
-// f32x2 instructions (two elements per issue slot).
-// FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
+// The four f32 operations per element are issued as packed f32x2 instructions (two elements per
+// issue slot); the int -> float and float -> u8 conversions use the 1.5 * 2^23 trick on the FMA
+// pipe. FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
 template <bool EDGE, bool FP8 = false, u32 N = 32>
-X17_DEV void softmax_chunk_v2(u32 const (&r)[N], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
+X17_DEV void softmax_chunk(u32 const (&r)[N], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
 							  f32 (&sum)[4], u32 (&pk)[N / 4]) {
 	using namespace attn_cfg;
 	u64 const s256 = pack_f32x2(256.0f, 256.0f);
@@ -183,8 +152,9 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 	}
 }
 
-#ifdef X17_EXPERIMENT_TIMING
-// timeline of one CTA, recorded in shared memory and copied out at the end:
+#ifdef X17_ATTN_TIMELINE
+// Diagnostic build (-DX17_ATTN_TIMELINE, never the shipped library): timeline of one CTA, recorded
+// in shared memory and copied out at the end, read back through x17ai_b200_experiment_times:
 // g_times[role][event] = clock64() << 8 | tag; roles: 0 TMA, 1 MMA, 2 row warp 2, 3 row warp 6
 __device__ long long g_times[4][128];
 __device__ unsigned g_ntimes[4];
@@ -233,7 +203,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 8));
 	volatile u32 *const abort_flag = tmem_slot_gen + 1;
 	WaitCtx const ctx{abort_flag, p.status};
-#ifdef X17_EXPERIMENT_TIMING
+#ifdef X17_ATTN_TIMELINE
 	long long *const t_buf = reinterpret_cast<long long *>(smem_gen + BAR_OFF + 256);
 	u32 t_n = 0;
 #endif
@@ -444,7 +414,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
 		bool ok = true;
 		u32 const col_base = half * 64u;
-#ifdef X17_EXPERIMENT_TIMING
+#ifdef X17_ATTN_TIMELINE
 		u32 const trole = warp == 2 ? 2u : 3u;
 		bool const tme = warp == 2 || warp == 6;
 #define X17_TR(tag) do { if (tme) X17_T(trole, tag); } while (0)
@@ -548,30 +518,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
 			if (edge) visible(k0, lo, span);
-#ifdef X17_EXPERIMENT_SMALL_LOOP
-			u32 const ta = tmem_base + lane_addr + col_base;
-			if (t > t_begin) {
-				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
-					ok = false;
-					break;
-				}
-			}
-#pragma unroll 1
-			for (u32 c = 0; c < 64; c += 16) {
-				u32 r[16];
-				tmem_ld_32x32b_x16(ta + c, r);
-				tmem_wait_ld();
-				u32 pk[4];
-				if (edge) {
-					softmax_chunk_v2<true, FP8PV, 16>(r, col_base + c, temp, neg_m, lo, span, sum, pk);
-				} else {
-					softmax_chunk_v2<false, FP8PV, 16>(r, col_base + c, temp, neg_m, lo, span, sum, pk);
-				}
-				st_shared_v4(p_row + (((ch0 + (c >> 4)) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
-			}
-			tc_fence_before();
-			mbar_arrive(s_done_bar(0));
-#else
 			u32 r0[32], r1[32];
 			u32 const ta = tmem_base + lane_addr + col_base;
 			tmem_ld_32x32b_x32(ta, r0);
@@ -582,11 +528,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			X17_TR(4);
 			u32 pk0[8], pk1[8];
 			if (edge) {
-				softmax_chunk_v2<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk_v2<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			} else {
-				softmax_chunk_v2<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk_v2<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
 			X17_TR(5);
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
@@ -599,11 +545,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			st_shared_v4(p_row + (((ch0 + 1) ^ sw) << 4), pk0[4], pk0[5], pk0[6], pk0[7]);
 			st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
 			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
-#endif
 			fence_proxy_async_smem();
 			mbar_arrive(p_ready_bar);
 			X17_TR(6);
-#ifndef X17_EXPERIMENT_SMALL_LOOP
 			if constexpr (DEBUG) {
 				if (row_ok) {
 					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
@@ -615,7 +559,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 					}
 				}
 			}
-#endif
 		}
 
 		// ---- normalise and store: each thread of the pair takes half of the D columns ----
@@ -690,7 +633,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		}
 	}
 
-#ifdef X17_EXPERIMENT_TIMING
+#ifdef X17_ATTN_TIMELINE
 	{
 		bool const sel = blockIdx.x == 20 && blockIdx.y == 3 && blockIdx.z == 0;
 		u32 const role = warp == 0 ? 0u : warp == 1 ? 1u : warp == 2 ? 2u : warp == 6 ? 3u : 9u;
