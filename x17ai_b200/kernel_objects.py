@@ -28,7 +28,9 @@ def build_rms_norm(model_dim: int, eps: float = 2.0 ** -70, force: bool = False)
     d = CACHE / f"rms_norm_{model_dim}"
     cubin, meta = d / "kernel.cubin", d / "meta.json"
     src = SRC / "rms_norm.cu"
-    if not force and cubin.exists() and meta.exists() and cubin.stat().st_mtime >= src.stat().st_mtime:
+    # the kernel object is rebuilt when its source or any header it includes is newer
+    newest = max(f.stat().st_mtime for f in (src, SRC.parent / "rms_norm.cuh", SRC.parent / "ptx.cuh"))
+    if not force and cubin.exists() and meta.exists() and cubin.stat().st_mtime >= newest:
         return d
     if model_dim % 16 != 0 or model_dim > 8192:
         raise X17Error(f"rms_norm kernel object requires MODEL_DIM to be a multiple of 16 and at most 8192, got {model_dim}")
