@@ -268,6 +268,12 @@ class GemmKernel:
                                             _ptr(c), _ptr(rrms), _ptr(residual)))
 
 
+def _proj_scale(inputs: int) -> float:
+    """inv_sqrt(inputs) / FIXED_I8_SCALE**2 with the reference's operations (sqrt, reciprocal, divide:
+    src/util.rs:20-24, src/main.rs:413-415), so that the constant is the same f64."""
+    return 1.0 / math.sqrt(float(inputs)) / (FIXED_I8_SCALE * FIXED_I8_SCALE)
+
+
 def qkvg_fwd_i8(stream, x, w_qkvg, n_heads, head_dim, q, kv, k_rrms, g=None, eps=2.0 ** -70):
     """Fused Q / KV / gate projection (attn_q_fwd + attn_kv_fwd of src/main.rs:387-491 in one launch)."""
     rows, model_dim = matrix_shape("qkvg", "x", x, (None, None), DTYPE_INT8)
@@ -279,7 +285,7 @@ def qkvg_fwd_i8(stream, x, w_qkvg, n_heads, head_dim, q, kv, k_rrms, g=None, eps
     matrix_shape("qkvg", "k_rrms", k_rrms, (rows, n_heads), DTYPE_F32)
     if g is not None:
         matrix_shape("qkvg", "g", g, (rows, gate_cols), DTYPE_INT8)
-    cfg = _lib.QkvgConfig(model_dim, n_heads, head_dim, gate_cols, model_dim ** -0.5 / 64.0, FIXED_I8_SCALE, eps)
+    cfg = _lib.QkvgConfig(model_dim, n_heads, head_dim, gate_cols, _proj_scale(model_dim), FIXED_I8_SCALE, eps)
     check(_lib.load().x17ai_b200_qkvg_fwd_i8(stream.handle, ctypes.byref(cfg), _ptr(x), rows, _ptr(w_qkvg), _ptr(q),
                                               _ptr(kv), _ptr(k_rrms), _ptr(g)))
 
@@ -308,22 +314,22 @@ def rms_norm(stream, mode, inp, out, row_scale=None, eps=2.0 ** -70):
 
 def attn_q_fwd_config(model_dim, q_outputs):
     return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_INT8, EPI_SCALE, model_dim, q_outputs,
-                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=FIXED_I8_SCALE)
+                      inp_scale=_proj_scale(model_dim), out_scale=FIXED_I8_SCALE)
 
 
 def attn_kv_fwd_config(model_dim, kv_outputs, head_dim, eps=2.0 ** -70):
     return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_INT8, EPI_RMS_NORM, model_dim, kv_outputs,
-                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=FIXED_I8_SCALE, eps=eps, head_dim=head_dim)
+                      inp_scale=_proj_scale(model_dim), out_scale=FIXED_I8_SCALE, eps=eps, head_dim=head_dim)
 
 
 def attn_y_fwd_config(attn_width, model_dim, c_dtype=DTYPE_E4M3):
     return GemmConfig(DTYPE_INT8, DTYPE_INT8, c_dtype, EPI_RESIDUAL, attn_width, 2 * model_dim,
-                      inp_scale=attn_width ** -0.5 / 64.0, out_scale=1.0)
+                      inp_scale=_proj_scale(attn_width), out_scale=1.0)
 
 
 def ffn_f_fwd_config(model_dim, f_width):
     return GemmConfig(DTYPE_INT8, DTYPE_INT8, DTYPE_E4M3, EPI_GEGLU, model_dim, 2 * f_width,
-                      inp_scale=model_dim ** -0.5 / 64.0, out_scale=1.0)
+                      inp_scale=_proj_scale(model_dim), out_scale=1.0)
 
 
 def ffn_y_fwd_f8_config(f_width, model_dim, b_dtype=DTYPE_INT8, c_dtype=DTYPE_E4M3):
