@@ -13,7 +13,9 @@ Follows the reference *kernel* (not its float64 PyTorch model) step by step:
     online_softmax                 :208-291   (running max, lazy rescale, un-rounded sum)
     combine_and_store              :293-351   (out = rint(clamp(O / sum)), L = log2(sum) + max)
   masks: keys j with i - W' <= j <= i - 1  (:79-134, :540-567), W' = W rounded up to 16
-The float64 model it is pinned against is new_block.py:162-232 (attn_one_head).
+Pinned twice: against the float64 model new_block.py:162-232 (attn_one_head) through the fixtures
+of tests/golden, and, with `kv_tile=16`, bit for bit against the reference kernel itself compiled
+for sm_100a (oracle/build_ref.py, tests/test_gpu_reference_kernel.py).
 
 `kv_tile` is the number of keys per online-softmax step.  The reference kernel uses 16
 (:65-66); a different tile changes when the running max moves and therefore which

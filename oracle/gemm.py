@@ -18,7 +18,9 @@ Reference functions restated (file:line):
                                                                  548-557,599-608,650-660
 Transcendentals use exact libm values where the kernels use the PTX `.approx`
 forms, so results agree with a GPU to within the last quantisation step, not bit
-for bit; everything integer is exact.
+for bit; everything integer is exact. Pinned against the fixtures of tests/golden and against
+the reference's own kernels compiled for sm_100a (oracle/build_ref.py,
+tests/test_gpu_reference_gemm.py: at most 1.4e-4 of the e4m3 bytes differ from them).
 """
 import math
 
