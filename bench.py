@@ -200,6 +200,48 @@ class AttnPrefill:
         return done_ops / dt, f"{heads} (sequence, head) units of S={S} D={D} W={W}, oracle kv_tile=16, {dt:.1f} s"
 
 
+class AttnPvFp8(AttnPrefill):
+    """configs[2]: the fp8 P.V variant on the prefill shape: int8 Q.K^T, P as e4m3, V as e4m3 with a per-head
+    f32 scale, f32 accumulation, bf16 output."""
+    name = "attention_pv_fp8_prefill"
+    dtype = "s8/e4m3"
+
+    def __init__(self, stream, device, B=8, H=32, S=8192, D=128, W=1024, seed=0):
+        super().__init__(stream, device, B, H, S, D, W, seed)
+        torch = self.torch
+        g = torch.Generator(device=device).manual_seed(seed + 1)
+        # V and the sink values as e4m3 bytes of N(0,1) values (OCP e4m3fn, the hardware's format)
+        v = torch.randn(B, S, H, D, generator=g, device=device).to(torch.float8_e4m3fn).view(torch.int8)
+        self.kv.view(B, S, H, 2, D)[:, :, :, 1, :] = v
+        self.sink_v8 = torch.randn(H, D, generator=g, device=device).to(torch.float8_e4m3fn).view(torch.uint8)
+        self.v_scale = (0.25 + torch.rand(H, generator=g, device=device)).float()
+        self.out = torch.empty(B, S, H * D, dtype=torch.bfloat16, device=device)
+        self.alg_bytes = self.q.numel() + self.kv.numel() + 2 * self.out.numel() + self.l.numel() * 4
+        self.config = dict(self.config, workload="configs[2] attention with fp8 P.V (e4m3 P and V, bf16 out)")
+        torch.cuda.synchronize()
+
+    def step(self):
+        self.kern.launch_pv_fp8(self.stream, self.q, self.kv, self.sink_k, self.sink_v8, self.temp, self.v_scale,
+                                self.out, self.l, self.W)
+
+    def host_buffers(self):
+        t = self.torch
+        self.h_q = self.q.cpu().pin_memory(); self.h_kv = self.kv.cpu().pin_memory()
+        self.h_out = t.empty_like(self.out, device="cpu").pin_memory()
+        self.h2d = self.h_q.numel() + self.h_kv.numel()
+        self.d2h = self.h_out.numel() * 2
+
+    def e2e_step(self):
+        s = self.stream
+        s.upload(self.h_q.data_ptr(), self.q.data_ptr(), 0, self.h_q.numel())
+        s.upload(self.h_kv.data_ptr(), self.kv.data_ptr(), 0, self.h_kv.numel())
+        self.step()
+        s.download(self.out.data_ptr(), self.h_out.data_ptr(), 0, self.h_out.numel() * 2)
+
+    def e2e_sync(self):
+        self.stream.synchronize()
+
+
 class Ffn:
     """configs[3]: gated FFN on 16384 tokens, d_model 4096, hidden 14336 (reference GeGLU form)."""
     bound = "tensor"
@@ -470,6 +512,7 @@ def _shape(args, n):
 
 WORKLOADS = {
     "attn": lambda s, d, a=None: AttnPrefill(s, d, *(_shape(a, 5) or ())),
+    "attn_pv_fp8": lambda s, d, a=None: AttnPvFp8(s, d, *(_shape(a, 5) or ())),
     "ffn_i8": lambda s, d, a=None: Ffn(s, d, False, *(_shape(a, 3) or ())),
     "ffn_f8": lambda s, d, a=None: Ffn(s, d, True, *(_shape(a, 3) or ())),
     "decode": lambda s, d, a=None: Decode(s, d, *(_shape(a, 5) or ())),
@@ -491,10 +534,11 @@ def run_reference(args, rank, world):
     except Exception:
         pass
     # build the workload description without touching a GPU
-    cls = {"attn": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode, "rms_norm": RmsNorm,
-           "block": Block}[args.workload]
+    cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode,
+           "rms_norm": RmsNorm, "block": Block}[args.workload]
     w = cls.__new__(cls)
-    if args.workload == "attn":
+    if args.workload in ("attn", "attn_pv_fp8"):
+        # the fp8 P.V variant has no CPU form of its own: the int8 restatement (same operation count) stands in
         w.S, w.D, w.W, B, H = 8192, 128, 1024, 8, 32
         cfg = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H, "seq_len": 8192,
                "head_dim": 128, "window": 1024}
@@ -664,7 +708,8 @@ def main():
     value = world * work * args.steps / dev_total / scale
     achieved = work / kernel_avg / scale
     line = {
-        "metric": {"attn": "int8 sliding-window attention prefill throughput", "ffn_i8": "gated FFN forward throughput",
+        "metric": {"attn": "int8 sliding-window attention prefill throughput",
+                   "attn_pv_fp8": "attention with fp8 P.V prefill throughput", "ffn_i8": "gated FFN forward throughput",
                    "ffn_f8": "gated FFN forward throughput", "decode": "int8 decode attention KV-cache bandwidth",
                    "rms_norm": "RMSNorm bandwidth", "block": "quantized block forward throughput"}[args.workload],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -681,7 +726,7 @@ def main():
     }
     if gather_ms is not None:
         line["gather_ms"] = gather_ms
-    if args.workload == "attn":
+    if args.workload in ("attn", "attn_pv_fp8"):
         line["reference_count_tops"] = world * w.ref_ops * args.steps / dev_total / 1e12
     if e2e is not None:
         e2e["value"] = world * work / (e2e["ms_per_step"] * 1e-3) / scale
