@@ -314,6 +314,68 @@ class Ffn:
         return ops / dt, f"{n} x {rows} token rows of the same FFN, {dt:.1f} s"
 
 
+class Qkvg:
+    """The fused Q / KV projection (one launch for attn_q_fwd + attn_kv_fwd of src/main.rs:387-491) at the
+    benchmark's model shape: scale -> FixedI8 for Q and V, per-head L2 norm for K, rrms side output."""
+    name = "qkvg_fwd_i8"
+    bound = "tensor"
+    dtype = "s8"
+
+    def __init__(self, stream, device, M=16384, Dm=4096, H=32, D=128, seed=0):
+        import torch
+        from x17ai_b200 import kernels as K
+        self.torch, self.stream, self.K = torch, stream, K
+        g = torch.Generator(device=device).manual_seed(seed)
+        codes = lambda *s: torch.clamp(torch.round(torch.randn(*s, generator=g, device=device) * 8.0), -127, 127).to(torch.int8)
+        hd = H * D
+        self.x, self.w = codes(M, Dm), codes(3 * hd, Dm)
+        self.q = torch.empty(M, hd, dtype=torch.int8, device=device)
+        self.kv = torch.empty(M, 2 * hd, dtype=torch.int8, device=device)
+        self.rrms = torch.empty(M, H, dtype=torch.float32, device=device)
+        self.H, self.D, self.M, self.Dm = H, D, M, Dm
+        self.ops = 2.0 * M * Dm * 3 * hd
+        self.tokens = M
+        self.units = M
+        self.alg_bytes = M * Dm + 3 * hd * Dm + 3 * M * hd + 4 * M * H
+        self.launches_per_step = 1
+        self.config = {"workload": "fused Q/KV projection", "tokens": M, "d_model": Dm, "n_heads": H, "head_dim": D,
+                       "l2": "x + weights + outputs %.0f MB larger than the 126 MB L2" % (self.alg_bytes / 1e6)}
+        torch.cuda.synchronize()
+
+    def step(self):
+        self.K.qkvg_fwd_i8(self.stream, self.x, self.w, self.H, self.D, self.q, self.kv, self.rrms)
+
+    def host_buffers(self):
+        t = self.torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_q = t.empty_like(self.q, device="cpu").pin_memory()
+        self.h_kv = t.empty_like(self.kv, device="cpu").pin_memory()
+        self.h2d, self.d2h = self.h_x.numel(), self.h_q.numel() + self.h_kv.numel()
+
+    def e2e_step(self):
+        s = self.stream
+        s.upload(self.h_x.data_ptr(), self.x.data_ptr(), 0, self.h_x.numel())
+        self.step()
+        s.download(self.q.data_ptr(), self.h_q.data_ptr(), 0, self.h_q.numel())
+        s.download(self.kv.data_ptr(), self.h_kv.data_ptr(), 0, self.h_kv.numel())
+
+    def cpu_sample(self, seconds_hint=10.0):
+        from oracle import gemm as o_gemm
+        H, D, Dm = self.H, self.D, self.Dm
+        rng = np.random.default_rng(0)
+        mk = lambda *s: np.clip(np.rint(rng.standard_normal(s) * 8), -127, 127).astype(np.int8)
+        x, wq, wkv = mk(512, Dm), mk(H * D, Dm), mk(2 * H * D, Dm)
+        t0, n = time.perf_counter(), 0
+        while True:
+            o_gemm.attn_q_fwd(x, wq)
+            o_gemm.attn_kv_fwd(x, wkv, D)
+            n += 1
+            if time.perf_counter() - t0 > seconds_hint:
+                break
+        dt = time.perf_counter() - t0
+        return n * 2.0 * 512 * Dm * 3 * H * D / dt, f"{n} x 512 token rows through both projections, {dt:.1f} s"
+
+
 class Decode:
     """configs[4] tail: batch 256, one new token each, int8 KV cache of 4096 tokens, 32 heads x 128."""
     name = "int8_decode_attention"
@@ -515,6 +577,7 @@ WORKLOADS = {
     "attn_pv_fp8": lambda s, d, a=None: AttnPvFp8(s, d, *(_shape(a, 5) or ())),
     "ffn_i8": lambda s, d, a=None: Ffn(s, d, False, *(_shape(a, 3) or ())),
     "ffn_f8": lambda s, d, a=None: Ffn(s, d, True, *(_shape(a, 3) or ())),
+    "qkvg": lambda s, d, a=None: Qkvg(s, d, *(_shape(a, 4) or ())),
     "decode": lambda s, d, a=None: Decode(s, d, *(_shape(a, 5) or ())),
     "rms_norm": lambda s, d, a=None: RmsNorm(s, d, *(_shape(a, 2) or ())),
     "block": lambda s, d, a=None: Block(s, d, *(_shape(a, 7) or ())),
@@ -535,7 +598,7 @@ def run_reference(args, rank, world):
         pass
     # build the workload description without touching a GPU
     cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode,
-           "rms_norm": RmsNorm, "block": Block}[args.workload]
+           "rms_norm": RmsNorm, "block": Block, "qkvg": Qkvg}[args.workload]
     w = cls.__new__(cls)
     if args.workload in ("attn", "attn_pv_fp8"):
         # the fp8 P.V variant has no CPU form of its own: the int8 restatement (same operation count) stands in
@@ -551,6 +614,10 @@ def run_reference(args, rank, world):
         w.D, w.T, w.W = 128, 4096, 4096
         cfg = {"workload": "configs[4] decode", "batch": 256, "n_heads": 32, "head_dim": 128, "kv_len": 4096}
         unit, metric = "GB/s", "int8 decode attention KV-cache bandwidth"
+    elif args.workload == "qkvg":
+        w.Dm, w.H, w.D = 4096, 32, 128
+        cfg = {"workload": "fused Q/KV projection", "tokens": 16384, "d_model": 4096, "n_heads": 32, "head_dim": 128}
+        unit, metric = "TOPS", "fused Q/KV projection throughput"
     elif args.workload == "block":
         w.Dm, w.H, w.D, w.F, w.W = 4096, 32, 128, 14336, 1024
         cfg = {"workload": "block forward: q/kv projection, int8 attention, attn_y, GeGLU FFN, ffn_y (e4m3 x int8)",
@@ -588,7 +655,7 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N > 1: also time an NCCL all_gather of the step's output "
                     "(reported separately as gather_ms; the path itself needs no collective)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
-                    "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W")
+                    "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W; qkvg M,Dm,H,D")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()
@@ -710,6 +777,7 @@ def main():
     line = {
         "metric": {"attn": "int8 sliding-window attention prefill throughput",
                    "attn_pv_fp8": "attention with fp8 P.V prefill throughput", "ffn_i8": "gated FFN forward throughput",
+                   "qkvg": "fused Q/KV projection throughput",
                    "ffn_f8": "gated FFN forward throughput", "decode": "int8 decode attention KV-cache bandwidth",
                    "rms_norm": "RMSNorm bandwidth", "block": "quantized block forward throughput"}[args.workload],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
