@@ -94,6 +94,11 @@ def test_reference_kernel_on_fixtures(stream, name):
     out, l = _run_ours(stream, q, kv, sk, sv, temp, H, D, W)
     hist = code_hist(out, ref_out)
     print(name, "this kernel vs reference kernel:", hist[:4], "of", out.size)
+    mine = code_hist(out, g["attn_out_i8"].reshape(S, H * D))
+    print(name, "this kernel vs float64 model:", mine[:7] / out.size)
+    # not further from the reference's float64 model than the reference's own kernel is
+    theirs = code_hist(ref_out, g["attn_out_i8"].reshape(S, H * D))
+    assert mine[2:].sum() <= theirs[2:].sum() * 1.05 + 8
     assert hist[2:].sum() == 0 and hist[1] / out.size <= 0.03
     assert np.max(np.abs(l - ref_l)) < 1e-3
 
