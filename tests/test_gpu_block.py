@@ -83,3 +83,66 @@ def test_block_forward_twice_is_stable(stream):
     stream.synchronize()
     for k in first:
         assert torch.equal(first[k], second[k]), k
+
+
+def test_block_from_reference_files(stream, tmp_path):
+    """The block built from safetensors files named as the reference's harness names them
+    (src/main.rs:39-71) equals the block built from the same tensors in memory."""
+    from x17ai_b200 import tensor_io
+    from x17ai_b200.block import BlockForward
+    g, c = load_golden("block_d64_w64")
+    S, Dm, D, H, F, W = c["S"], c["Dm"], c["D"], c["H"], c["F"], c["W"]
+    shapes = {"x_i8": (S, Dm), "attn_q_weights_i8": (H * D, Dm), "attn_kv_weights_i8": (H, 2 * D, Dm),
+              "attn_y_weights_i8": (2 * Dm, H * D), "ffn_f_weights_i8": (2 * F, Dm), "ffn_y_weights_i8": (2 * Dm, F),
+              "sinks_k_i8": (H, D), "sinks_v_i8": (H, D), "attn_temperature_f32": (H,)}
+    for name, shape in shapes.items():
+        tensor_io.write_safetensors_file(tmp_path / f"{name}.safetensors", torch.from_numpy(g[name].reshape(shape)), name)
+    blk, x = BlockForward.from_directory(stream, tmp_path, H, D, W)
+    assert blk.config.model_dim == Dm and blk.config.ffn_width == F and tuple(x.shape) == (S, Dm)
+    got = {k: v.clone() for k, v in blk.forward(x).items()}
+    stream.synchronize()
+    ref_blk, ref_x = _block(stream, g, c, False)
+    want = ref_blk.forward(ref_x)
+    stream.synchronize()
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+    # the output files of the reference's harness (src/main.rs:273-280), read back with the safetensors package
+    from safetensors.torch import load_file
+    blk.save_outputs(tmp_path / "out", blk.forward(x))
+    q = load_file(str(tmp_path / "out" / "q_i8.safetensors"))["tensor"]
+    assert np.array_equal(q.numpy(), g["q_i8"].reshape(S, H * D))
+    kv = load_file(str(tmp_path / "out" / "kv_i8.safetensors"))["tensor"]
+    assert tuple(kv.shape) == (S, H, 2, D) and torch.equal(kv.reshape(S, -1), want["kv"].cpu())
+    y = load_file(str(tmp_path / "out" / "ffn_y_f8.safetensors"))["tensor"]
+    assert y.dtype == torch.float8_e4m3fn and torch.equal(y.view(torch.uint8), want["ffn_y"].cpu())
+    with pytest.raises(Exception, match="requires a CPU tensor"):
+        tensor_io.write_safetensors_file(tmp_path / "dev.safetensors", want["q"])
+
+
+def test_block_harness_writes_what_it_reports(tmp_path):
+    """`python -m x17ai_b200.block_main` on fixture files: the report names every launch of
+    src/main.rs:355-372 and the stored files hold the fixtures' projections."""
+    import io
+    from safetensors.torch import load_file
+    from x17ai_b200 import block_main, tensor_io
+    g, c = load_golden("block_d128_w128")
+    S, Dm, D, H, F, W = c["S"], c["Dm"], c["D"], c["H"], c["F"], c["W"]
+    shapes = {"x_i8": (S, Dm), "attn_q_weights_i8": (H * D, Dm), "attn_kv_weights_i8": (2 * H * D, Dm),
+              "attn_y_weights_i8": (2 * Dm, H * D), "ffn_f_weights_i8": (2 * F, Dm), "ffn_y_weights_i8": (2 * Dm, F),
+              "sinks_k_i8": (H, D), "sinks_v_i8": (H, D), "attn_temperature_f32": (H,)}
+    for name, shape in shapes.items():
+        tensor_io.write_safetensors_file(tmp_path / "in" / f"{name}.safetensors", torch.from_numpy(g[name].reshape(shape)))
+    for fused in (False, True):
+        if fused and (H * D) % 256 != 0:
+            continue
+        text = io.StringIO()
+        seconds = block_main.run(tmp_path / "in", tmp_path / "out", H, D, W, fused_qkv=fused, out=text)
+        report = text.getvalue()
+        for name in (("qkvg_fwd_i8",) if fused else ("attn_q_fwd", "attn_kv_fwd")) + ("attn_fwd_i8", "attn_y_fwd", "ffn_f_fwd", "ffn_y_fwd_f8"):
+            assert f"\t{name} in " in report, report
+        assert all(v > 0 for k, v in seconds.items() if not (fused and k == "attn_kv"))
+        q = load_file(str(tmp_path / "out" / "q_i8.safetensors"))["tensor"].numpy()
+        assert np.array_equal(q, g["q_i8"].reshape(S, H * D))
+        f8 = load_file(str(tmp_path / "out" / "ffn_f_f8.safetensors"))["tensor"].view(torch.uint8).numpy()
+        assert (f8 != g["ffn_f_f8"].reshape(S, F)).mean() <= 1e-3
+    assert block_main.main([str(tmp_path / "nowhere"), str(tmp_path / "out"), "--heads", "2", "--head-dim", "128"]) == 1

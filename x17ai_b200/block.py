@@ -52,7 +52,7 @@ class BlockForward:
         hd = c.attn_width
         if fused_qkv and hd % 256 != 0:
             raise K.X17Error(f"fused_qkv needs n_heads * head_dim to be a multiple of 256, got {hd}")
-        self.w_q, self.w_kv, self.w_attn_y, self.w_ffn_f = w_q, w_kv, w_attn_y, w_ffn_f
+        self.w_q, self.w_kv, self.w_attn_y, self.w_ffn_f, self.w_ffn_y = w_q, w_kv, w_attn_y, w_ffn_f, w_ffn_y
         self.sink_k, self.sink_v, self.attn_temperature = sink_k, sink_v, attn_temperature
         self.k_q = K.GemmKernel(K.attn_q_fwd_config(c.model_dim, hd))
         self.k_kv = K.GemmKernel(K.attn_kv_fwd_config(c.model_dim, 2 * hd, c.head_dim))
@@ -67,6 +67,59 @@ class BlockForward:
         stream.synchronize()
         self._rows = 0
         self._timers = None
+
+    # file names of the reference's harness (src/main.rs:39-71)
+    FILES = {"w_q": "attn_q_weights_i8", "w_kv": "attn_kv_weights_i8", "w_attn_y": "attn_y_weights_i8",
+             "w_ffn_f": "ffn_f_weights_i8", "w_ffn_y": "ffn_y_weights_i8", "sink_k": "sinks_k_i8",
+             "sink_v": "sinks_v_i8", "attn_temperature": "attn_temperature_f32"}
+
+    @classmethod
+    def from_directory(cls, stream, directory, n_heads: int, head_dim: int, window_size: int, fused_qkv: bool = False):
+        """Builds the block from the safetensors files the reference's harness reads (one tensor per
+        file, `<name>.safetensors`), inferring model_dim and the FFN width from the weight shapes with
+        the checks of validate_*_inputs (src/main.rs:257-385). Returns (block, x) with the input
+        sequence `x_i8.safetensors` uploaded too when it exists, else x is None."""
+        from pathlib import Path
+        from . import tensor_io
+        d = Path(directory)
+        t = {k: tensor_io.load_to_device(d / f"{name}.safetensors", stream) for k, name in cls.FILES.items()}
+        hd = n_heads * head_dim
+        w_q = t["w_q"]
+        if w_q.dim() != 2 or w_q.shape[0] != hd:
+            raise K.X17Error(f"attn_q weights must be [{hd}, model_dim], got {list(w_q.shape)}")
+        model_dim = w_q.shape[1]
+        w_kv = t["w_kv"].reshape(2 * hd, model_dim)          # main.rs:82 flattens the KV weights the same way
+        w_attn_y = t["w_attn_y"].reshape(2 * model_dim, hd)
+        w_ffn_f = t["w_ffn_f"]
+        if w_ffn_f.dim() != 2 or w_ffn_f.shape[1] != model_dim or w_ffn_f.shape[0] % 2 != 0:
+            raise K.X17Error(f"ffn_f weights must be [2 * ffn_width, {model_dim}], got {list(w_ffn_f.shape)}")
+        ffn_width = w_ffn_f.shape[0] // 2
+        w_ffn_y = t["w_ffn_y"].reshape(2 * model_dim, ffn_width)
+        blk = cls(stream, BlockConfig(model_dim, n_heads, head_dim, ffn_width, window_size), w_q, w_kv, w_attn_y, w_ffn_f,
+                  w_ffn_y, t["sink_k"].reshape(n_heads, head_dim), t["sink_v"].reshape(n_heads, head_dim),
+                  t["attn_temperature"].reshape(n_heads), fused_qkv=fused_qkv)
+        x_path = d / "x_i8.safetensors"
+        x = tensor_io.load_to_device(x_path, stream).reshape(-1, model_dim) if x_path.exists() else None
+        return blk, x
+
+    # output file names and dtypes' suffixes of the reference's harness (src/main.rs:273-280)
+    OUTPUT_FILES = {"q": "q_i8", "kv": "kv_i8", "k_rrms": "k_rrms_f32", "attn_out": "attn_out_i8", "attn_l": "attn_l_f32",
+                    "attn_y": "attn_y_f8", "ffn_f": "ffn_f_f8", "ffn_y": "ffn_y_f8"}
+
+    def save_outputs(self, directory, out: dict) -> None:
+        """Downloads the tensors forward() returned and writes them as the reference's harness does
+        (src/main.rs:255-280): one file per tensor, KV as [rows, heads, 2, head_dim], e4m3 tensors as
+        F8_E4M3."""
+        from pathlib import Path
+        from . import tensor_io
+        c = self.config
+        for key, name in self.OUTPUT_FILES.items():
+            host = tensor_io.download(out[key], self.stream)
+            if key == "kv":
+                host = host.reshape(-1, c.n_heads, 2, c.head_dim)
+            if name.endswith("_f8"):
+                host = host.view(torch.float8_e4m3fn)
+            tensor_io.write_safetensors_file(Path(directory) / f"{name}.safetensors", host)
 
     def _buffers(self, rows: int, device):
         if rows == self._rows:
