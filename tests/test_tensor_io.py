@@ -59,3 +59,36 @@ def test_writer_creates_the_directory_and_names_the_tensor(tmp_path):
     empty = tmp_path / "empty.safetensors"
     tensor_io.write_safetensors_file(empty, torch.zeros(0, 4, dtype=torch.int8))
     assert tuple(tensor_io.read_safetensors_file(empty).shape) == (0, 4)
+
+
+def test_named_tensor_files_bin_and_safetensors(tmp_path):
+    """The name's tag declares the storage type (block_utils.py:51-83); raw files are the bytes alone."""
+    from safetensors.torch import load_file
+    from x17ai_b200 import X17Error, tensor_io
+    g = torch.Generator().manual_seed(1)
+    cases = {"q_i8": torch.randint(-127, 128, (6, 8), generator=g, dtype=torch.int8),
+             "ffn_f_f8": torch.randn(6, 8, generator=g).to(torch.float8_e4m3fn),
+             "attn_l_f32": torch.randn(2, 6, generator=g), "acc_i32": torch.randint(-9, 9, (3, 4), generator=g, dtype=torch.int32),
+             "x_bf16": torch.randn(4, 4, generator=g).to(torch.bfloat16)}
+    for stem, t in cases.items():
+        for ext in (".bin", ".safetensors"):
+            p = tmp_path / (stem + ext)
+            assert tensor_io.storage_dtype(p) == t.dtype
+            tensor_io.write_tensor_file(p, t)
+            back = tensor_io.read_tensor_file(p, t.shape)
+            assert back.dtype == t.dtype and torch.equal(back.view(torch.uint8), t.view(torch.uint8))
+        assert (tmp_path / (stem + ".bin")).read_bytes() == t.view(torch.uint8).numpy().tobytes()
+        # the reference's Python side names the tensor after the file without its tag (block_utils.py:104-107)
+        assert list(load_file(str(tmp_path / (stem + ".safetensors")))) == [stem.rpartition("_")[0]]
+    assert tuple(tensor_io.read_tensor_file(tmp_path / "q_i8.bin", (-1, 4)).shape) == (12, 4)
+    with pytest.raises(X17Error, match="dtype tag"):
+        tensor_io.storage_dtype("weights.bin")
+    with pytest.raises(X17Error, match="extension"):
+        tensor_io.storage_dtype("weights_i8.npy")
+    with pytest.raises(X17Error, match="declares"):
+        tensor_io.write_tensor_file(tmp_path / "q_f32.bin", cases["q_i8"])
+    with pytest.raises(X17Error, match="do not fit"):
+        tensor_io.read_tensor_file(tmp_path / "q_i8.bin", (5, 5))
+    (tmp_path / "odd_f32.bin").write_bytes(b"\x00" * 6)
+    with pytest.raises(X17Error, match="whole number"):
+        tensor_io.read_tensor_file(tmp_path / "odd_f32.bin")

@@ -1,7 +1,11 @@
 """Tensors in and out of safetensors files, the way the reference's host reads its inputs
 (Tensor::from_safetensors_file, src/tensor.rs:155-179: one tensor per file, uploaded as it is).
 
-The format is parsed here directly (8-byte little-endian header length, JSON header with dtype,
+Raw `.bin` files (the bytes of the tensor and nothing else) follow the naming rule of the
+reference's Python side: the storage type is the tag before the extension, `_i8`, `_f8`, `_f32`,
+`_i32` or `_bf16` (block_utils.py:51-83), and the shape is the caller's.
+
+The safetensors format is parsed here directly (8-byte little-endian header length, JSON header with dtype,
 shape and byte offsets, raw little-endian data), so the package needs no extra dependency; the
 tests check the reader and writer against the `safetensors` package.
 """
@@ -93,3 +97,60 @@ def download(tensor: torch.Tensor, stream) -> torch.Tensor:
     stream.download(src.data_ptr(), host.data_ptr(), 0, src.numel() * src.element_size())
     stream.synchronize()
     return host
+
+
+# storage type tag in a tensor file's name (block_utils.py:51-58)
+_TAGS = {"i8": torch.int8, "f8": torch.float8_e4m3fn, "f32": torch.float32, "i32": torch.int32, "bf16": torch.bfloat16}
+
+
+def storage_dtype(file_name) -> torch.dtype:
+    """`attn_out_i8.safetensors` -> torch.int8: the tag after the last underscore of the stem names the
+    storage type; `.bin` and `.safetensors` are the two extensions (block_utils.py:60-83)."""
+    p = Path(file_name)
+    if p.suffix not in (".bin", ".safetensors"):
+        raise X17Error(f"unsupported tensor file extension {p.suffix!r} in {str(file_name)!r}")
+    base, sep, tag = p.stem.rpartition("_")
+    if not sep or not base or tag not in _TAGS:
+        raise X17Error(f"tensor file name must end with a dtype tag (_i8, _f8, _f32, _i32, _bf16): {str(file_name)!r}")
+    return _TAGS[tag]
+
+
+def read_tensor_file(path, shape=None) -> torch.Tensor:
+    """A `.safetensors` or raw `.bin` tensor file as a host tensor of the type its name declares. A raw
+    file needs `shape` (one dimension may be -1); for a safetensors file `shape`, when given, reshapes."""
+    dtype = storage_dtype(path)
+    if Path(path).suffix == ".safetensors":
+        t = read_safetensors_file(path)
+        if t.dtype != dtype:
+            raise X17Error(f"{path} declares {dtype} by name but holds {t.dtype}")
+    else:
+        try:
+            raw = Path(path).read_bytes()
+        except OSError as e:
+            raise X17Error(f"cannot read tensor file {path}: {e.strerror}") from e
+        item = torch.empty(0, dtype=dtype).element_size()
+        if len(raw) % item != 0:
+            raise X17Error(f"{path}: {len(raw)} bytes is not a whole number of {dtype} elements")
+        t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(dtype) if raw else torch.empty(0, dtype=dtype)
+    if shape is not None:
+        try:
+            t = t.reshape(shape)
+        except RuntimeError as e:
+            raise X17Error(f"{path}: {t.numel()} elements do not fit shape {list(shape)}") from e
+    return t
+
+
+def write_tensor_file(path, tensor: torch.Tensor) -> None:
+    """The counterpart of read_tensor_file: the extension picks the format, the name's tag must match
+    the tensor's type (store_tensor_with_dtype, block_utils.py:139-186, refuses a mismatch too)."""
+    dtype = storage_dtype(path)
+    if tensor.dtype != dtype:
+        raise X17Error(f"tensor file name {str(path)!r} declares {dtype}, the tensor is {tensor.dtype}")
+    if Path(path).suffix == ".safetensors":
+        write_safetensors_file(path, tensor, Path(path).stem.rpartition("_")[0])
+        return
+    if tensor.device.type != "cpu":
+        raise X17Error("write_tensor_file requires a CPU tensor; download it first")
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    t = tensor.detach().contiguous()
+    Path(path).write_bytes(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
