@@ -358,6 +358,26 @@ x17ai_DiagnosticBuffer *x17ai_b200_read_status(x17ai_CudaStreamHandle *stream, u
  * bytes written.  diag may be NULL (returns 0). */
 size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_t cap);
 
+/* Stream capture. The reference's host issues the block's launches one by one (src/main.rs:193-255)
+ * and has no graph object; a host that replays the same launches many times (the same buffers,
+ * new contents) records them once between graph_begin and graph_end and replays them with
+ * graph_launch, one driver call per block instead of six.
+ *   - Between begin and end only this library's launch entry points and x17ai_cuda_upload_data /
+ *     x17ai_cuda_download_data on page-locked memory may be called on the stream; anything that
+ *     synchronises (x17ai_cuda_synchronize, read_status, timers' elapsed time) invalidates the
+ *     capture and graph_end then returns a diagnostic.
+ *   - Every kernel of the sequence must have been launched once on the device before begin (the
+ *     first launch of an entry point sets function attributes and per-device state).
+ *   - The graph holds the pointers and sizes of the recorded calls, not the data.
+ *   - graph_destroy and graph_launch take the stream to enter its context. */
+typedef struct x17ai_b200_Graph x17ai_b200_Graph;
+x17ai_DiagnosticBuffer *x17ai_b200_graph_begin(x17ai_CudaStreamHandle *stream);
+x17ai_DiagnosticBuffer *x17ai_b200_graph_end(x17ai_CudaStreamHandle *stream, x17ai_b200_Graph **graph);
+x17ai_DiagnosticBuffer *x17ai_b200_graph_launch(x17ai_b200_Graph *graph, x17ai_CudaStreamHandle *stream);
+x17ai_DiagnosticBuffer *x17ai_b200_graph_destroy(x17ai_b200_Graph *graph, x17ai_CudaStreamHandle *stream);
+/* Kernel launches one replay of the graph performs (added to x17ai_b200_launch_count per replay). */
+uint64_t x17ai_b200_graph_kernel_nodes(x17ai_b200_Graph const *graph);
+
 /* Number of kernel launches this library has issued since it was loaded (all entry points). */
 uint64_t x17ai_b200_launch_count(void);
 

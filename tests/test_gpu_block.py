@@ -146,3 +146,39 @@ def test_block_harness_writes_what_it_reports(tmp_path):
         f8 = load_file(str(tmp_path / "out" / "ffn_f_f8.safetensors"))["tensor"].view(torch.uint8).numpy()
         assert (f8 != g["ffn_f_f8"].reshape(S, F)).mean() <= 1e-3
     assert block_main.main([str(tmp_path / "nowhere"), str(tmp_path / "out"), "--heads", "2", "--head-dim", "128"]) == 1
+
+
+def test_block_graph_replay(stream):
+    """The six launches recorded once and replayed (x17ai_b200_graph_*): a replay on new input in the
+    same buffer equals a plain forward on that input, and counts its kernels as launches."""
+    import x17ai_b200
+    from x17ai_b200 import X17Error
+    from x17ai_b200.device import CudaGraph
+    lib = x17ai_b200.load()
+    g, c = load_golden("block_d128_w128")
+    for fused in (False, True):
+        blk, x = _block(stream, g, c, fused)
+        with pytest.raises(X17Error, match="capture"):
+            blk.replay()
+        blk.capture(x)
+        n = blk._graph.kernel_nodes
+        assert n == (5 if fused else 6)
+        x2 = torch.roll(x, shifts=3, dims=0).contiguous()
+        want = {k: v.clone() for k, v in blk.forward(x2).items()}
+        stream.synchronize()
+        x.copy_(x2)
+        torch.cuda.synchronize()
+        before = lib.x17ai_b200_launch_count()
+        blk.replay()
+        stream.synchronize()
+        assert lib.x17ai_b200_launch_count() - before == n
+        for k, v in want.items():
+            assert torch.equal(getattr(blk, k), v), k
+    # a synchronising call inside the recording invalidates it; the error is reported, the stream stays usable
+    with pytest.raises(X17Error):
+        with CudaGraph(stream):
+            blk.forward(x)
+            stream.synchronize()
+    out = blk.forward(x)
+    stream.synchronize()
+    assert torch.equal(out["q"], want["q"])

@@ -108,6 +108,11 @@ SIGNATURES = {
     "x17ai_b200_rms_norm": (DIAG, [c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_double]),
     "x17ai_b200_read_status": (DIAG, [c_void_p, POINTER(c_uint32)]),
     "x17ai_b200_take_diagnostic": (c_size_t, [DIAG, c_char_p, c_size_t]),
+    "x17ai_b200_graph_begin": (DIAG, [c_void_p]),
+    "x17ai_b200_graph_end": (DIAG, [c_void_p, POINTER(c_void_p)]),
+    "x17ai_b200_graph_launch": (DIAG, [c_void_p, c_void_p]),
+    "x17ai_b200_graph_destroy": (DIAG, [c_void_p, c_void_p]),
+    "x17ai_b200_graph_kernel_nodes": (c_uint64, [c_void_p]),
     "x17ai_b200_launch_count": (c_uint64, []),
 }
 

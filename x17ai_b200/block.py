@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import torch
 
 from . import kernels as K
-from .device import CudaTimer
+from .device import CudaGraph, CudaTimer
 
 
 @dataclass(frozen=True)
@@ -67,6 +67,8 @@ class BlockForward:
         stream.synchronize()
         self._rows = 0
         self._timers = None
+        self._graph = None
+        self._graph_x = None
 
     # file names of the reference's harness (src/main.rs:39-71)
     FILES = {"w_q": "attn_q_weights_i8", "w_kv": "attn_kv_weights_i8", "w_attn_y": "attn_y_weights_i8",
@@ -120,6 +122,24 @@ class BlockForward:
             if name.endswith("_f8"):
                 host = host.view(torch.float8_e4m3fn)
             tensor_io.write_safetensors_file(Path(directory) / f"{name}.safetensors", host)
+
+    def capture(self, x) -> dict:
+        """Records the launches of forward(x) as one graph; replay() then re-runs them on whatever `x`
+        and the weights hold at that moment (same buffers, one driver call). Runs forward(x) once
+        first so that no kernel is launched for the first time inside the recording."""
+        out = self.forward(x)
+        self.stream.synchronize()
+        if self._graph is not None:
+            self._graph.destroy()
+        with CudaGraph(self.stream) as g:
+            self.forward(x)
+        self._graph, self._graph_x = g, x
+        return out
+
+    def replay(self) -> None:
+        if self._graph is None:
+            raise K.X17Error("BlockForward.replay(): capture(x) first")
+        self._graph.launch()
 
     def _buffers(self, rows: int, device):
         if rows == self._rows:

@@ -9,6 +9,9 @@
 #include <cmath>
 #include <cstdint>
 #include <mutex>
+#include <new>
+#include <unordered_map>
+#include <vector>
 
 #include "attn.cuh"
 #include "decode.cuh"
@@ -22,6 +25,8 @@ using x17::static_diag;
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
+std::mutex g_capture_mutex;
+std::unordered_map<void *, CUcontext> g_capture_ctx;   // streams between graph_begin and graph_end
 
 // ---- per-device state -----------------------------------------------------------------------
 
@@ -446,6 +451,109 @@ x17ai_DiagnosticBuffer *x17ai_b200_read_status(x17ai_CudaStreamHandle *stream, u
 	}
 	return nullptr;
 }
+
+// ---- stream capture: a sequence of this library's launches replayed as one CUDA graph ---------
+
+struct x17ai_b200_Graph {
+	cudaGraphExec_t exec = nullptr;
+	uint64_t kernel_nodes = 0;
+};
+
+x17ai_DiagnosticBuffer *x17ai_b200_graph_begin(x17ai_CudaStreamHandle *stream) {
+	char const *who = "x17ai_b200_graph_begin()";
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	cudaError_t e = cudaStreamBeginCapture(reinterpret_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal);
+	if (e != cudaSuccess) {
+		return make_diag("x17ai_b200_graph_begin(): failed", who, ": cannot begin capture: ", cudaGetErrorString(e));
+	}
+	// an invalidated capture no longer answers cuStreamGetCtx: graph_end finds the context here
+	std::lock_guard<std::mutex> lock(g_capture_mutex);
+	g_capture_ctx[stream] = scope.ctx;
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_graph_end(x17ai_CudaStreamHandle *stream, x17ai_b200_Graph **graph) {
+	char const *who = "x17ai_b200_graph_end()";
+	if (graph == nullptr) return static_diag("x17ai_b200_graph_end(): null argument");
+	*graph = nullptr;
+	if (stream == nullptr) return static_diag("x17ai_b200_graph_end(): null stream");
+	CUcontext ctx = nullptr;
+	{
+		std::lock_guard<std::mutex> lock(g_capture_mutex);
+		auto it = g_capture_ctx.find(stream);
+		if (it == g_capture_ctx.end()) return static_diag("x17ai_b200_graph_end(): no capture was begun on this stream");
+		ctx = it->second;
+		g_capture_ctx.erase(it);
+	}
+	struct Pushed {
+		bool ok;
+		explicit Pushed(CUcontext c) : ok(DRV(cuCtxPushCurrent)(c) == CUDA_SUCCESS) {}
+		~Pushed() {
+			CUcontext popped = nullptr;
+			if (ok) DRV(cuCtxPopCurrent)(&popped);
+		}
+	} pushed(ctx);
+	if (!pushed.ok) return static_diag("x17ai_b200_graph_end(): cannot enter the stream's context");
+	cudaGraph_t g = nullptr;
+	cudaError_t e = cudaStreamEndCapture(reinterpret_cast<cudaStream_t>(stream), &g);
+	if (e != cudaSuccess || g == nullptr) {
+		cudaGetLastError();   // ending an invalidated capture returns the stream to normal use
+		return make_diag("x17ai_b200_graph_end(): failed", who, ": the capture was invalidated: ",
+						 cudaGetErrorString(e));
+	}
+	size_t n = 0;
+	uint64_t kernels = 0;
+	if (cudaGraphGetNodes(g, nullptr, &n) == cudaSuccess && n > 0) {
+		std::vector<cudaGraphNode_t> nodes(n);
+		if (cudaGraphGetNodes(g, nodes.data(), &n) == cudaSuccess) {
+			for (size_t i = 0; i < n; ++i) {
+				cudaGraphNodeType t;
+				if (cudaGraphNodeGetType(nodes[i], &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++kernels;
+			}
+		}
+	}
+	cudaGraphExec_t exec = nullptr;
+	e = cudaGraphInstantiate(&exec, g, 0);
+	cudaGraphDestroy(g);
+	if (e != cudaSuccess) {
+		return make_diag("x17ai_b200_graph_end(): failed", who, ": cannot instantiate the graph: ", cudaGetErrorString(e));
+	}
+	auto *out = new (std::nothrow) x17ai_b200_Graph;
+	if (out == nullptr) {
+		cudaGraphExecDestroy(exec);
+		return static_diag("x17ai_b200_graph_end(): out of memory");
+	}
+	out->exec = exec;
+	out->kernel_nodes = kernels;
+	*graph = out;
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_graph_launch(x17ai_b200_Graph *graph, x17ai_CudaStreamHandle *stream) {
+	char const *who = "x17ai_b200_graph_launch()";
+	if (graph == nullptr || graph->exec == nullptr) return static_diag("x17ai_b200_graph_launch(): null graph");
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	cudaError_t e = cudaGraphLaunch(graph->exec, reinterpret_cast<cudaStream_t>(stream));
+	if (e != cudaSuccess) {
+		return make_diag("x17ai_b200_graph_launch(): failed", who, ": graph launch failed: ", cudaGetErrorString(e));
+	}
+	g_launches.fetch_add(graph->kernel_nodes, std::memory_order_relaxed);
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_graph_destroy(x17ai_b200_Graph *graph, x17ai_CudaStreamHandle *stream) {
+	char const *who = "x17ai_b200_graph_destroy()";
+	if (graph == nullptr) return nullptr;
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	if (graph->exec != nullptr) cudaGraphExecDestroy(graph->exec);
+	delete graph;
+	return nullptr;
+}
+
+uint64_t x17ai_b200_graph_kernel_nodes(x17ai_b200_Graph const *graph) { return graph ? graph->kernel_nodes : 0; }
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_meta(x17ai_AttnConfig const *cfg, x17ai_AttnMeta *meta) {
 	char const *who = "x17ai_b200_attn_meta()";

@@ -107,3 +107,48 @@ class CudaTimer:
         if self.handle:
             check(self._lib.x17ai_cuda_destroy_timer(self.handle))
             self.handle = None
+
+
+class CudaGraph:
+    """A recorded sequence of this library's launches on one stream, replayed with one driver call
+    (x17ai_b200_graph_begin / _end / _launch). Use as a context manager around the launches to record:
+
+        with CudaGraph(stream) as g:
+            kernel.launch(stream, ...)
+        g.launch()
+    """
+
+    def __init__(self, stream: CudaStream):
+        self._lib = _lib.load()
+        self.stream = stream
+        self.handle = None
+
+    def __enter__(self):
+        check(self._lib.x17ai_b200_graph_begin(self.stream.handle))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        out = ctypes.c_void_p()
+        diag = self._lib.x17ai_b200_graph_end(self.stream.handle, ctypes.byref(out))
+        if exc_type is None:
+            check(diag)
+            self.handle = out.value
+        elif diag:   # the body failed: drop the end-of-capture diagnostic, the body's error is the one to report
+            _lib.take_diag(diag)
+        elif out.value:
+            check(self._lib.x17ai_b200_graph_destroy(out.value, self.stream.handle))
+        return False
+
+    @property
+    def kernel_nodes(self) -> int:
+        return int(self._lib.x17ai_b200_graph_kernel_nodes(self.handle))
+
+    def launch(self) -> None:
+        if self.handle is None:
+            raise _lib.X17Error("CudaGraph.launch(): nothing was recorded")
+        check(self._lib.x17ai_b200_graph_launch(self.handle, self.stream.handle))
+
+    def destroy(self) -> None:
+        if self.handle is not None:
+            h, self.handle = self.handle, None
+            check(self._lib.x17ai_b200_graph_destroy(h, self.stream.handle))
