@@ -55,12 +55,7 @@ namespace attn_cfg {
 constexpr u32 BQ = 128;   // queries per CTA
 constexpr u32 BKV = 128;  // keys per tile
 constexpr u32 STAGES = 4;
-#ifndef X17_ATTN_PARTS
-#define X17_ATTN_PARTS 2
-#endif
-constexpr u32 PARTS = X17_ATTN_PARTS;     // threads per query row; each takes BKV / PARTS score columns
-constexpr u32 PART_COLS = BKV / PARTS;
-constexpr u32 ROW_WARPS = 4 * PARTS;
+constexpr u32 ROW_WARPS = 8;
 constexpr u32 ROW_THREADS = ROW_WARPS * 32;
 constexpr u32 THREADS = 64 + ROW_THREADS;
 constexpr u32 TMEM_COLS = 256;
@@ -383,12 +378,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 	} else {
 		// ---------------- two threads per query row ----------------
 		u32 const quarter = warp & 3;          // TMEM lanes this warp may touch
-		u32 const half = (warp - 2) >> 2;      // which PART_COLS score columns; parts 0 and 1 also take half of D each
+		u32 const half = (warp - 2) >> 2;      // which 64 score columns / which half of D
 		u32 const row = quarter * 32 + lane;
 		u32 const qi = q0 + row;
 		bool const row_ok = qi < p.seq_len;
 		u32 const lane_addr = (quarter * 32u) << 16;
 		u32 const xid = half * BQ + row;       // own slot in the exchange area
+		u32 const xpartner = (half ^ 1u) * BQ + row;
 
 		// sink score: exact int32 dot product of this row's q with sink_k
 		i32 sink_dot = 0;
@@ -417,7 +413,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
 		bool ok = true;
-		u32 const col_base = half * PART_COLS;
+		u32 const col_base = half * 64u;
 #ifdef X17_ATTN_TIMELINE
 		u32 const trole = warp == 2 ? 2u : 3u;
 		bool const tme = warp == 2 || warp == 6;
@@ -457,7 +453,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			u32 r0[32], r1[32];
 			u32 const ta = tmem_base + lane_addr + b * BKV + col_base;
 			tmem_ld_32x32b_x32(ta, r0);
-			if constexpr (PARTS == 2) tmem_ld_32x32b_x32(ta + 32, r1);
+			tmem_ld_32x32b_x32(ta + 32, r1);
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
@@ -465,18 +461,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			if (edge) {
 				if (pos_t) {
 					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
-					if constexpr (PARTS == 2) extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
+					extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
 				} else {
 					extreme_chunk<true, false>(r0, col_base, lo, span, ext);
-					if constexpr (PARTS == 2) extreme_chunk<true, false>(r1, col_base + 32, lo, span, ext);
+					extreme_chunk<true, false>(r1, col_base + 32, lo, span, ext);
 				}
 			} else {
 				if (pos_t) {
 					extreme_chunk<false, true>(r0, col_base, lo, span, ext);
-					if constexpr (PARTS == 2) extreme_chunk<false, true>(r1, col_base + 32, lo, span, ext);
+					extreme_chunk<false, true>(r1, col_base + 32, lo, span, ext);
 				} else {
 					extreme_chunk<false, false>(r0, col_base, lo, span, ext);
-					if constexpr (PARTS == 2) extreme_chunk<false, false>(r1, col_base + 32, lo, span, ext);
+					extreme_chunk<false, false>(r1, col_base + 32, lo, span, ext);
 				}
 			}
 			if constexpr (DEBUG) {
@@ -486,9 +482,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
 					for (u32 i = 0; i < 32; ++i) {
 						if (k0 + col_base + i < p.seq_len) dst[i] = i32(r0[i]);
-						if constexpr (PARTS == 2) {
-							if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = i32(r1[i]);
-						}
+						if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = i32(r1[i]);
 					}
 				}
 			}
@@ -502,9 +496,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		}
 		xchg[xid] = cand;
 		named_barrier_sync(1, ROW_THREADS);
-		f32 m = sink_s;
-#pragma unroll
-		for (u32 k = 0; k < PARTS; ++k) m = fmaxf(m, xchg[k * BQ + row]);
+		f32 const m = fmaxf(sink_s, fmaxf(cand, xchg[xpartner]));
 		named_barrier_sync(1, ROW_THREADS);  // the exchange area is reused for the sums
 
 		// ---- sweep 2: probabilities against the final maximum ----
@@ -512,7 +504,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		f32 sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 		u32 const p_row = s_p + row * 128u;
 		u32 const sw = row & 7u;
-		u32 const ch0 = half * (PART_COLS / 16);  // first of this thread's 16-byte chunks
+		u32 const ch0 = half * 4u;  // first of this thread's four 16-byte chunks
 		#pragma unroll 1
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			if (!mbar_wait_warp(s_full_bar(0), use0 & 1, ctx, ST_WAIT_S_FULL, t)) {
@@ -529,7 +521,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			u32 r0[32], r1[32];
 			u32 const ta = tmem_base + lane_addr + col_base;
 			tmem_ld_32x32b_x32(ta, r0);
-			if constexpr (PARTS == 2) tmem_ld_32x32b_x32(ta + 32, r1);
+			tmem_ld_32x32b_x32(ta + 32, r1);
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
@@ -537,10 +529,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			u32 pk0[8], pk1[8];
 			if (edge) {
 				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				if constexpr (PARTS == 2) softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			} else {
 				softmax_chunk<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				if constexpr (PARTS == 2) softmax_chunk<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+				softmax_chunk<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
 			X17_TR(5);
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
@@ -551,10 +543,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 			}
 			st_shared_v4(p_row + (((ch0 + 0) ^ sw) << 4), pk0[0], pk0[1], pk0[2], pk0[3]);
 			st_shared_v4(p_row + (((ch0 + 1) ^ sw) << 4), pk0[4], pk0[5], pk0[6], pk0[7]);
-			if constexpr (PARTS == 2) {
-				st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
-				st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
-			}
+			st_shared_v4(p_row + (((ch0 + 2) ^ sw) << 4), pk1[0], pk1[1], pk1[2], pk1[3]);
+			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
 			fence_proxy_async_smem();
 			mbar_arrive(p_ready_bar);
 			X17_TR(6);
@@ -565,9 +555,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
 					for (u32 i = 0; i < 32; ++i) {
 						if (k0 + col_base + i < p.seq_len) dst[i] = u8(pk0[i >> 2] >> (8 * (i & 3)));
-						if constexpr (PARTS == 2) {
-							if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = u8(pk1[i >> 2] >> (8 * (i & 3)));
-						}
+						if (k0 + col_base + 32 + i < p.seq_len) dst[32 + i] = u8(pk1[i >> 2] >> (8 * (i & 3)));
 					}
 				}
 			}
@@ -577,11 +565,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		f32 const part = __fadd_rn(__fadd_rn(sum[0], sum[1]), __fadd_rn(sum[2], sum[3]));
 		xchg[xid] = part;
 		named_barrier_sync(1, ROW_THREADS);
-		f32 both = xchg[row];   // the parts in column order, the same sum in every thread of the row
-#pragma unroll
-		for (u32 k = 1; k < PARTS; ++k) both = __fadd_rn(both, xchg[k * BQ + row]);
+		f32 const other = xchg[xpartner];
+		f32 const both = half == 0 ? __fadd_rn(part, other) : __fadd_rn(other, part);
 		X17_TR(7);
-		if (ok && half < 2 && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
+		if (ok && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
 			tc_fence_after();
 			X17_TR(8);
 			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
