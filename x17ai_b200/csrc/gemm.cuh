@@ -100,6 +100,22 @@ X17_DEV f32 acc_to_f32(u32 bits) {
 
 // ---- kernel ----------------------------------------------------------------------------------
 
+// Tile order of the persistent loop: groups of GROUP_M row tiles; inside a group the row tiles run
+// fastest and every column tile is visited before the next group starts. The tiles in flight on
+// the 148 CTAs then cover a near-square patch of C (16 row tiles x ~9 column tiles) instead of
+// every row tile of one column tile, so a wave touches far fewer distinct rows of A and B and
+// they stay in L2 while the wave needs them.
+X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx) {
+	constexpr u32 GROUP_M = 16;
+	u32 const per_group = GROUP_M * tiles_n;
+	u32 const g = t / per_group;
+	u32 const first_m = g * GROUP_M;
+	u32 const rows = min(GROUP_M, tiles_m - first_m);   // the last group may be short
+	u32 const r = t - g * per_group;
+	m_idx = first_m + r % rows;
+	n_idx = r / rows;
+}
+
 template <int EPI, bool F8>
 __global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -155,8 +171,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 			u32 it = 0;
 			bool ok = true;
 			for (u32 t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-				i32 const m0 = i32((t % p.tiles_m) * BM);
-				i32 const n0 = i32((t / p.tiles_m) * BN);
+				u32 tm, tn;
+				tile_origin(t, p.tiles_m, p.tiles_n, tm, tn);
+				i32 const m0 = i32(tm * BM);
+				i32 const n0 = i32(tn * BN);
 				for (u32 kb = 0; kb < k_blocks; ++kb, ++it) {
 					u32 const s = it % STAGES;
 					u32 const ph = (it / STAGES) & 1;
@@ -223,8 +241,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 		for (u32 t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local_tile) {
 			u32 const buf = local_tile & 1;
 			u32 const acc_ph = (local_tile >> 1) & 1;
-			u32 const m0 = (t % p.tiles_m) * BM;
-			u32 const n0 = (t / p.tiles_m) * BN;
+			u32 tm, tn;
+			tile_origin(t, p.tiles_m, p.tiles_n, tm, tn);
+			u32 const m0 = tm * BM;
+			u32 const n0 = tn * BN;
 			if (!mbar_wait_warp(acc_full_bar(buf), acc_ph, ctx, ST_WAIT_ACC_FULL, buf)) {
 				ok = false;
 				break;
