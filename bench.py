@@ -520,7 +520,22 @@ class Block:
                        "fused_qkv": fused, "l2": "weights 0.42 GB + activations per sequence 0.4 GB, larger than the 126 MB L2"}
         torch.cuda.synchronize()
 
+    def make_sequential(self):
+        """--sequential: the eight-launch form (RMSNorm before each sub-block) on an e4m3 hidden state."""
+        t = self.torch
+        self.sequential = True
+        self.h = t.empty((self.B, self.S, self.Dm), dtype=t.uint8, device=self.x.device)
+        for b in range(self.B):   # a hidden state of the block's own making
+            self.h[b].copy_(self.blk.forward(self.x[b])["ffn_y"])
+        t.cuda.synchronize()
+        self.launches_per_step += 2 * self.B
+        self.config["form"] = "sequential: RMSNorm -> attention sub-block -> RMSNorm -> FFN sub-block"
+
     def step(self):
+        if getattr(self, "sequential", False):
+            for b in range(self.B):
+                self.blk.forward_layer(self.h[b])
+            return
         for b in range(self.B):
             self.blk.forward(self.x[b])
 
@@ -654,6 +669,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--gather", action="store_true", help="N > 1: also time an NCCL all_gather of the step's output "
                     "(reported separately as gather_ms; the path itself needs no collective)")
+    ap.add_argument("--sequential", action="store_true", help="block workload: RMSNorm before each sub-block (eight launches)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
                     "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W; qkvg M,Dm,H,D")
     args = ap.parse_args()
@@ -675,6 +691,11 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     stream = device.CudaStream(local)
     w = WORKLOADS[args.workload](stream, dev, args)
+    if args.sequential:
+        if args.workload != "block":
+            raise SystemExit("--sequential applies to --workload block")
+        w.make_sequential()
+        args.no_e2e = True   # the end-to-end leg times the harness form only
 
     def barrier():
         stream.synchronize()

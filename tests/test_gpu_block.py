@@ -182,3 +182,44 @@ def test_block_graph_replay(stream):
     out = blk.forward(x)
     stream.synchronize()
     assert torch.equal(out["q"], want["q"])
+
+
+@pytest.mark.parametrize("name", ["block_d64_w64", "block_d128_w128"])
+def test_layer_sequential_form(stream, name):
+    """forward_layer: RMSNorm -> attention sub-block -> RMSNorm -> FFN sub-block, two layers chained through
+    the e4m3 hidden state; every stage against the oracle applied to the tensor the device fed it."""
+    from oracle import rms_norm as o_rms
+    g, c = load_golden(name)
+    S, Dm, D, H, F, W = c["S"], c["Dm"], c["D"], c["H"], c["F"], c["W"]
+    blk, _ = _block(stream, g, c, False)
+    h = torch.from_numpy(g["ffn_y_f8"].reshape(S, Dm).copy()).cuda()   # an e4m3 hidden state of the model's own making
+    torch.cuda.synchronize()
+    for layer in range(2):
+        out = blk.forward_layer(h)
+        stream.synchronize()
+        got = {k: v.cpu().numpy() for k, v in out.items()}
+        h_np = h.cpu().numpy()
+        ref = o_rms.rms_norm_e4m3_i8(h_np)
+        dd = np.abs(got["x_attn"].astype(np.int32) - ref.astype(np.int32))
+        assert dd.max() <= 1 and (dd > 0).mean() <= 2e-3
+        x = got["x_attn"]
+        assert np.array_equal(got["q"], o_gemm.attn_q_fwd(x, g["attn_q_weights_i8"].reshape(H * D, Dm)))
+        kv_ref, _ = o_gemm.attn_kv_fwd(x, g["attn_kv_weights_i8"].reshape(2 * H * D, Dm), D)
+        dd = np.abs(got["kv"].astype(np.int32) - kv_ref.astype(np.int32))
+        assert dd.max() <= 1 and (dd > 0).mean() <= 1e-4
+        ao, _ = o_attn.attn_fwd_i8(got["q"], got["kv"], g["sinks_k_i8"].reshape(H, D), g["sinks_v_i8"].reshape(H, D),
+                                   g["attn_temperature_f32"].reshape(H), W, H, D, kv_tile=1 << 20)
+        hist = code_hist(got["attn_out"], ao)
+        assert hist[2:].sum() == 0 and hist[1] / ao.size <= 0.02
+        ref = o_gemm.attn_y_fwd(got["attn_out"], g["attn_y_weights_i8"].reshape(2 * Dm, H * D), x)
+        assert (got["attn_y"] != ref).mean() <= 2e-3
+        ref = o_rms.rms_norm_e4m3_i8(got["attn_y"])
+        dd = np.abs(got["x_ffn"].astype(np.int32) - ref.astype(np.int32))
+        assert dd.max() <= 1 and (dd > 0).mean() <= 2e-3
+        x2 = got["x_ffn"]
+        ref = o_gemm.ffn_f_fwd(x2, g["ffn_f_weights_i8"].reshape(2 * F, Dm))
+        assert (got["ffn_f"] != ref).mean() <= 2e-3
+        ref = o_gemm.ffn_y_fwd_f8(got["ffn_f"], g["ffn_y_weights_i8"].reshape(2 * Dm, F), x2)
+        assert (got["ffn_y"] != ref).mean() <= 2e-3
+        h = out["ffn_y"].clone()   # the next layer's hidden state
+        torch.cuda.synchronize()

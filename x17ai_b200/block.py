@@ -123,6 +123,33 @@ class BlockForward:
                 host = host.view(torch.float8_e4m3fn)
             tensor_io.write_safetensors_file(Path(directory) / f"{name}.safetensors", host)
 
+    def forward_layer(self, h) -> dict:
+        """The sequential form of the layer, eight launches: the hidden state `h` [rows, model_dim] e4m3
+        is normalised (Rms_norm::kernel, rms_norm.cu:55-113: e4m3 in, FixedI8 out), goes through the
+        attention sub-block with itself as the residual, and the sub-block's e4m3 output is normalised
+        again and goes through the FFN sub-block the same way. The reference's harness feeds one x to
+        both sub-blocks (src/main.rs:193-255, forward()); this is the order the two formats imply,
+        every sub-block reading FixedI8 and writing e4m3. Returns forward()'s tensors plus the two
+        normalised inputs; `ffn_y` is the next layer's `h`."""
+        c, s = self.config, self.stream
+        rows, _ = K.matrix_shape("block", "h", h, (None, c.model_dim), K.DTYPE_E4M3)
+        self._buffers(rows, h.device)
+        K.rms_norm(s, K.RMS_E4M3_FIXED, h, self.x_attn)
+        x = self.x_attn
+        if self.fused_qkv:
+            K.qkvg_fwd_i8(s, x, self.w_qkv, c.n_heads, c.head_dim, self.q, self.kv, self.k_rrms)
+        else:
+            self.k_q.launch(s, x, self.w_q, self.q)
+            self.k_kv.launch(s, x, self.w_kv, self.kv, rrms=self.k_rrms)
+        self.k_attn.launch(s, self.q, self.kv, self.sink_k, self.sink_v, self.attn_temperature, self.attn_out,
+                           self.attn_l, c.window_size)
+        self.k_attn_y.launch(s, self.attn_out, self.w_attn_y, self.attn_y, residual=x)
+        K.rms_norm(s, K.RMS_E4M3_FIXED, self.attn_y, self.x_ffn)
+        self.k_ffn_f.launch(s, self.x_ffn, self.w_ffn_f, self.ffn_f)
+        self.k_ffn_y.launch(s, self.ffn_f, self.w_ffn_y_split, self.ffn_y, residual=self.x_ffn)
+        return {"x_attn": self.x_attn, "q": self.q, "kv": self.kv, "k_rrms": self.k_rrms, "attn_out": self.attn_out,
+                "attn_l": self.attn_l, "attn_y": self.attn_y, "x_ffn": self.x_ffn, "ffn_f": self.ffn_f, "ffn_y": self.ffn_y}
+
     def capture(self, x) -> dict:
         """Records the launches of forward(x) as one graph; replay() then re-runs them on whatever `x`
         and the weights hold at that moment (same buffers, one driver call). Runs forward(x) once
@@ -154,6 +181,8 @@ class BlockForward:
         self.attn_y = e(rows, c.model_dim, dtype=torch.uint8)
         self.ffn_f = e(rows, c.ffn_width, dtype=torch.uint8)
         self.ffn_y = e(rows, c.model_dim, dtype=torch.uint8)
+        self.x_attn = e(rows, c.model_dim, dtype=torch.int8)   # forward_layer: RMSNorm of the incoming hidden state
+        self.x_ffn = e(rows, c.model_dim, dtype=torch.int8)    # forward_layer: RMSNorm of attn_y
         torch.cuda.synchronize(device)
         self._rows = rows
 
