@@ -347,6 +347,21 @@ x17ai_DiagnosticBuffer *x17ai_b200_rms_norm(
 	x17ai_CudaStreamHandle *stream, int32_t mode, void const *inp, size_t rows, size_t cols,
 	int8_t *out, float *row_scale, double eps);
 
+/* What a builder of a GEMM kernel object (kernel.cubin + meta.json in the reference's form,
+ * templates/basic_gemm/kernel.cu:9-16, kernel_build.rs:38-134) needs for one configuration: the
+ * epilogue constants as this library computes them, the launch metadata, and templates of the two
+ * TMA tensor maps (shape, strides, box, swizzle final; base address and A's row count are patched
+ * by the kernel object on the device at launch). int8 x int8 configurations only. */
+typedef struct x17ai_GemmObjectDesc {
+	int32_t epilogue_kind;
+	uint32_t n_raw, k, head_dim, rrms_cols;
+	uint64_t c_stride, resid_stride;
+	float k0, k1, k2, k3, k4;
+	uint32_t smem_bytes, threads, m_per_block, n_per_block;
+	uint8_t map_a[128], map_b[128];
+} x17ai_GemmObjectDesc;
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg, x17ai_GemmObjectDesc *desc);
+
 /* Device-side status of the kernels launched so far on the stream's device: synchronises the
  * stream, copies the four status words (0 = ok; else code << 16 | detail of the first bounded
  * wait that ran out, the reporting block, the number of reports, reserved) and clears them. */

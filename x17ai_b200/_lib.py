@@ -56,6 +56,14 @@ class GemmConfig(Structure):
                 ("eps", c_double), ("head_dim", c_size_t)]
 
 
+class GemmObjectDesc(Structure):
+    _fields_ = [("epilogue_kind", c_int32), ("n_raw", c_uint32), ("k", c_uint32), ("head_dim", c_uint32),
+                ("rrms_cols", c_uint32), ("c_stride", c_uint64), ("resid_stride", c_uint64),
+                ("k0", c_uint32), ("k1", c_uint32), ("k2", c_uint32), ("k3", c_uint32), ("k4", c_uint32),   # f32 bit patterns
+                ("smem_bytes", c_uint32), ("threads", c_uint32), ("m_per_block", c_uint32), ("n_per_block", c_uint32),
+                ("map_a", c_uint8 * 128), ("map_b", c_uint8 * 128)]
+
+
 class QkvgConfig(Structure):
     _fields_ = [("model_dim", c_size_t), ("n_heads", c_size_t), ("head_dim", c_size_t), ("gate_cols", c_size_t),
                 ("inp_scale", c_double), ("out_scale", c_double), ("eps", c_double)]
@@ -113,6 +121,7 @@ SIGNATURES = {
     "x17ai_b200_graph_launch": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_destroy": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_kernel_nodes": (c_uint64, [c_void_p]),
+    "x17ai_b200_gemm_object_desc": (DIAG, [POINTER(GemmConfig), POINTER(GemmObjectDesc)]),
     "x17ai_b200_launch_count": (c_uint64, []),
 }
 

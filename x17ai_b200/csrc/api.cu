@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstring>
 #include <mutex>
 #include <new>
 #include <unordered_map>
@@ -331,6 +332,54 @@ x17ai_DiagnosticBuffer *plan_gemm(x17ai_GemmConfig const *cfg, GemmPlan *plan, c
 	return nullptr;
 }
 
+// Shape and epilogue constants of one GEMM configuration (everything of GemmParams but the pointers).
+void fill_gemm_params(x17ai_GemmConfig const *cfg, GemmPlan const &plan, size_t a_rows, x17::GemmParams &p) {
+	using namespace x17::gemm_cfg;
+	size_t const k_a = cfg->a_cols;
+	size_t const k_total = plan.split ? 2 * k_a : k_a;
+	p.m = uint32_t(a_rows);
+	p.n_raw = uint32_t(cfg->b_rows);
+	p.k = uint32_t(k_total);
+	p.k_a = uint32_t(k_a);
+	p.tiles_m = uint32_t((a_rows + BM - 1) / BM);
+	p.tiles_n = uint32_t((cfg->b_rows + BN - 1) / BN);
+	p.head_dim = uint32_t(cfg->head_dim);
+	double const inp = cfg->inp_scale, out = cfg->out_scale;
+	switch (plan.epi) {
+	case x17::EPI_SCALE_I8:
+	case x17::EPI_RAW_I32:
+		p.c_stride = cfg->b_rows;
+		p.k0 = float(inp * out);
+		break;
+	case x17::EPI_L2NORM_KV:
+		p.c_stride = cfg->b_rows;
+		p.rrms_cols = uint32_t(cfg->b_rows / (2 * cfg->head_dim));
+		p.k0 = float(cfg->eps);
+		p.k1 = float(out * std::sqrt(double(cfg->head_dim)));  // gemm.rs:146
+		p.k2 = float(inp * out);                               // gemm.rs:152
+		break;
+	case x17::EPI_GEGLU_E4M3: {
+		// math::fast::gelu<INP^2, INP^2 * OUT^2, 1> (cuda/utils_core.cuh:426-448)
+		p.c_stride = cfg->b_rows / 2;
+		double const inp2 = inp * inp;
+		double const ck = std::sqrt(inp2 * 2.0 / M_PI);
+		p.k0 = float(0.044715 * ck * inp2);
+		p.k1 = float(ck);
+		p.k2 = float(0.5 * std::sqrt(inp2 * out * out) * std::sqrt(inp2));
+		break;
+	}
+	default:  // residual (cuda/gemm_b8.cuh:484-505, cuda/utils_core.cuh:397-405,468-483)
+		p.c_stride = cfg->b_rows / 2;
+		p.resid_stride = cfg->b_rows / 2;
+		p.k0 = float(0.5 * (1.0 / 8.0));
+		p.k1 = float(M_LN2 * -inp);
+		p.k2 = float(inp * 2.0);
+		p.k3 = float(inp * out / 2.0);
+		p.k4 = float(inp * inp * out);
+		break;
+	}
+}
+
 template <int EPI>
 cudaError_t gemm_go(bool f8, dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
 					x17::GemmParams const &p) {
@@ -434,6 +483,55 @@ int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
 	return int(e);
 }
 #endif
+
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg, x17ai_GemmObjectDesc *desc) {
+	char const *who = "x17ai_b200_gemm_object_desc()";
+	if (desc == nullptr) return static_diag("x17ai_b200_gemm_object_desc(): null argument");
+	GemmPlan plan{};
+	if (auto *d = plan_gemm(cfg, &plan, who)) return d;
+	if (plan.f8) {
+		return make_diag("x17ai_b200: unsupported kernel object", who,
+						 ": kernel objects exist for int8 x int8 GEMMs (the split e4m3 weight planes are not what the reference's host passes)");
+	}
+	if (!x17::driver().ok) {
+		return make_diag("x17ai_b200: CUDA driver not available", who, ": the CUDA driver is not available on this machine (",
+						 x17::driver().missing, " not found)");
+	}
+	using namespace x17::gemm_cfg;
+	x17::GemmParams p{};
+	fill_gemm_params(cfg, plan, BM, p);
+	std::memset(desc, 0, sizeof(*desc));
+	desc->epilogue_kind = plan.epi;
+	desc->n_raw = p.n_raw;
+	desc->k = p.k;
+	desc->head_dim = p.head_dim;
+	desc->rrms_cols = p.rrms_cols;
+	desc->c_stride = p.c_stride;
+	desc->resid_stride = p.resid_stride;
+	desc->k0 = p.k0;
+	desc->k1 = p.k1;
+	desc->k2 = p.k2;
+	desc->k3 = p.k3;
+	desc->k4 = p.k4;
+	desc->smem_bytes = SMEM_BYTES;
+	desc->threads = THREADS;
+	desc->m_per_block = BM;
+	desc->n_per_block = BN;
+	// templates of the two tensor maps: shape, strides, box and swizzle are final, the base address and
+	// A's row count are written by the kernel object itself at launch
+	void *const dummy = reinterpret_cast<void *>(uintptr_t(1) << 20);
+	CUtensorMap ta, tb;
+	CUresult e = make_map_2d(&ta, dummy, cfg->a_cols, BM, cfg->a_cols, BK, BM);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, dummy, cfg->a_cols, cfg->b_rows, cfg->a_cols, BK, BN);
+	if (e != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who, ": cuTensorMapEncodeTiled failed: ",
+						 x17::cu_error_text(e));
+	}
+	static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+	std::memcpy(desc->map_a, &ta, 128);
+	std::memcpy(desc->map_b, &tb, 128);
+	return nullptr;
+}
 
 uint64_t x17ai_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -836,51 +934,11 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
 	}
 	x17::GemmParams p{};
-	p.m = uint32_t(a_rows);
-	p.n_raw = uint32_t(cfg->b_rows);
-	p.k = uint32_t(k_total);
-	p.k_a = uint32_t(k_a);
-	p.tiles_m = uint32_t((a_rows + BM - 1) / BM);
-	p.tiles_n = uint32_t((cfg->b_rows + BN - 1) / BN);
+	fill_gemm_params(cfg, plan, a_rows, p);
 	p.c = c;
 	p.residual = residual;
 	p.rrms = rrms;
-	p.head_dim = uint32_t(cfg->head_dim);
 	p.status = scope.state().status;
-	double const inp = cfg->inp_scale, out = cfg->out_scale;
-	switch (plan.epi) {
-	case x17::EPI_SCALE_I8:
-	case x17::EPI_RAW_I32:
-		p.c_stride = cfg->b_rows;
-		p.k0 = float(inp * out);
-		break;
-	case x17::EPI_L2NORM_KV:
-		p.c_stride = cfg->b_rows;
-		p.rrms_cols = uint32_t(cfg->b_rows / (2 * cfg->head_dim));
-		p.k0 = float(cfg->eps);
-		p.k1 = float(out * std::sqrt(double(cfg->head_dim)));  // gemm.rs:146
-		p.k2 = float(inp * out);                               // gemm.rs:152
-		break;
-	case x17::EPI_GEGLU_E4M3: {
-		// math::fast::gelu<INP^2, INP^2 * OUT^2, 1> (cuda/utils_core.cuh:426-448)
-		p.c_stride = cfg->b_rows / 2;
-		double const inp2 = inp * inp;
-		double const ck = std::sqrt(inp2 * 2.0 / M_PI);
-		p.k0 = float(0.044715 * ck * inp2);
-		p.k1 = float(ck);
-		p.k2 = float(0.5 * std::sqrt(inp2 * out * out) * std::sqrt(inp2));
-		break;
-	}
-	default:  // residual (cuda/gemm_b8.cuh:484-505, cuda/utils_core.cuh:397-405,468-483)
-		p.c_stride = cfg->b_rows / 2;
-		p.resid_stride = cfg->b_rows / 2;
-		p.k0 = float(0.5 * (1.0 / 8.0));
-		p.k1 = float(M_LN2 * -inp);
-		p.k2 = float(inp * 2.0);
-		p.k3 = float(inp * out / 2.0);
-		p.k4 = float(inp * inp * out);
-		break;
-	}
 	uint32_t const n_tiles = p.tiles_m * p.tiles_n;
 	uint32_t const ctas = n_tiles < uint32_t(scope.state().sm_count) ? n_tiles : uint32_t(scope.state().sm_count);
 	dim3 grid(ctas);

@@ -116,11 +116,14 @@ X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx
 	n_idx = r / rows;
 }
 
+// The kernel proper. The tensor maps are reached through pointers: kernel parameters for the library's
+// entry points, maps patched on the device for the kernel objects (kernel_objects/gemm.cu). The loop
+// strides over the tiles by the number of CTAs of the launch, whatever the grid's shape.
 template <int EPI, bool F8>
-__global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-			const GemmParams p) {
+X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr, GemmParams const &p) {
 	using namespace gemm_cfg;
+	u32 const cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+	u32 const n_ctas = gridDim.x * gridDim.y * gridDim.z;
 	extern __shared__ u8 smem_raw[];
 	u32 const smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	u8 *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -166,11 +169,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 	if (warp == 0) {
 		// ---------------- TMA producer ----------------
 		if (elect_one()) {
-			tma_prefetch_desc(&tm_a);
-			tma_prefetch_desc(&tm_b);
+			tma_prefetch_desc(tm_a_ptr);
+			tma_prefetch_desc(tm_b_ptr);
 			u32 it = 0;
 			bool ok = true;
-			for (u32 t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+			for (u32 t = cta; t < n_tiles && ok; t += n_ctas) {
 				u32 tm, tn;
 				tile_origin(t, p.tiles_m, p.tiles_n, tm, tn);
 				i32 const m0 = i32(tm * BM);
@@ -184,8 +187,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 					}
 					mbar_expect_tx(full_bar(s), STAGE_BYTES);
 					u32 const a_dst = smem_base + s * STAGE_BYTES;
-					tma_load_2d(a_dst, &tm_a, full_bar(s), i32((kb * BK) % p.k_a), m0);
-					tma_load_2d(a_dst + A_BYTES, &tm_b, full_bar(s), i32(kb * BK), n0);
+					tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32((kb * BK) % p.k_a), m0);
+					tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
 				}
 			}
 		}
@@ -197,7 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 			u32 it = 0;
 			u32 local_tile = 0;
 			bool ok = true;
-			for (u32 t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local_tile) {
+			for (u32 t = cta; t < n_tiles && ok; t += n_ctas, ++local_tile) {
 				u32 const buf = local_tile & 1;
 				u32 const acc_ph = (local_tile >> 1) & 1;
 				if (!mbar_wait(acc_empty_bar(buf), acc_ph ^ 1, ctx, ST_WAIT_ACC_EMPTY, buf)) {
@@ -238,7 +241,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 		u32 const row_in_tile = quarter * 32 + lane;
 		u32 local_tile = 0;
 		bool ok = true;
-		for (u32 t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local_tile) {
+		for (u32 t = cta; t < n_tiles && ok; t += n_ctas, ++local_tile) {
 			u32 const buf = local_tile & 1;
 			u32 const acc_ph = (local_tile >> 1) & 1;
 			u32 tm, tn;
@@ -461,6 +464,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 		tc_fence_after();
 		tmem_dealloc(tmem_base, 512);
 	}
+}
+
+template <int EPI, bool F8>
+__global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+			const GemmParams p) {
+	gemm_body<EPI, F8>(&tm_a, &tm_b, p);
 }
 
 }  // namespace x17

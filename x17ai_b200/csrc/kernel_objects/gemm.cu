@@ -1,0 +1,115 @@
+// GEMM kernel object in the reference's form (templates/basic_gemm/kernel.cu:9-16): a cubin that exports
+//   extern "C" kernel(A *a, usize a_rows, B *b, usize b_rows, C *c [, f32 *rrms] [, i8 *residual])
+// with the shape and the epilogue constants fixed at compile time, loaded with x17ai_cuda_load_module /
+// x17ai_cuda_get_kernel and launched by the reference's host with its own grid
+// (c_rows / M_PER_BLOCK, raw_cols / N_PER_BLOCK, 1), gemm.rs:591-641.
+//
+// The tcgen05 GEMM reads its operands through TMA tensor maps, which only the driver can encode and
+// which the reference's argument list has no room for. The builder therefore bakes templates of the two
+// maps into this file (X17_MAP_A / X17_MAP_B: shape, strides, box and swizzle final) and every CTA
+// finishes them on the device: it copies the templates to shared memory, writes the base addresses it
+// was given and A's row count with tensormap.replace, publishes them to a slot in global memory owned by
+// its SM (one CTA per SM: the kernel's shared memory does not leave room for two) and acquires them for
+// the TMA unit.
+//
+// Compile with -DX17_EPI=<epilogue id> -DX17_N_RAW= -DX17_K= -DX17_HEAD_DIM= -DX17_RRMS_COLS= -DX17_C_STRIDE=
+// -DX17_RESID_STRIDE= -DX17_K0..X17_K4=<float bit patterns> and -include a header defining X17_MAP_A, X17_MAP_B.
+#include "../gemm.cuh"
+
+namespace {
+
+struct alignas(128) MapBytes {
+	unsigned char b[128];
+};
+
+__constant__ MapBytes c_map_a = {{X17_MAP_A}};
+__constant__ MapBytes c_map_b = {{X17_MAP_B}};
+__device__ MapBytes g_maps[256][2];   // slot per SM
+__device__ unsigned g_status[4];
+
+__device__ __forceinline__ void map_set_address(unsigned smem_map, void const *ptr) {
+	asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"l"(
+					 static_cast<unsigned long long>(smem_map)),
+				 "l"(ptr)
+				 : "memory");
+}
+__device__ __forceinline__ void map_set_rows(unsigned smem_map, unsigned rows) {
+	asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 1, %1;" ::"l"(
+					 static_cast<unsigned long long>(smem_map)),
+				 "r"(rows)
+				 : "memory");
+}
+
+}  // namespace
+
+extern "C" __global__ void __launch_bounds__(x17::gemm_cfg::THREADS, 1)
+kernel(void const *a, unsigned long long a_rows, void const *b, unsigned long long b_rows, void *c
+#if X17_EPI == 1
+	   , float *rrms
+#endif
+#if X17_EPI == 3 || X17_EPI == 4
+	   , signed char const *residual
+#endif
+) {
+	using namespace x17;
+	(void)b_rows;   // fixed at compile time (X17_N_RAW), as in the reference's templates
+	__shared__ MapBytes s_maps[2];
+
+	unsigned smid;
+	asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+	MapBytes *const slot = g_maps[smid & 255u];
+
+	if (threadIdx.x < 32) {
+		// templates -> shared memory (16 bytes per lane), patch, publish to this SM's slot
+		unsigned const lane = threadIdx.x;
+		uint4 const *src = reinterpret_cast<uint4 const *>(lane < 8 ? c_map_a.b : c_map_b.b) + (lane & 7u);
+		if (lane < 16) reinterpret_cast<uint4 *>(s_maps[lane >> 3].b)[lane & 7u] = *src;
+		__syncwarp();
+		if (lane == 0) {
+			unsigned const ma = smem_u32(s_maps[0].b), mb = smem_u32(s_maps[1].b);
+			map_set_address(ma, a);
+			map_set_rows(ma, static_cast<unsigned>(a_rows));
+			map_set_address(mb, b);
+		}
+		__syncwarp();
+		for (unsigned i = 0; i < 2; ++i) {
+			asm volatile(
+				"tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"
+				::"l"(reinterpret_cast<unsigned long long>(slot[i].b)), "r"(smem_u32(s_maps[i].b))
+				: "memory");
+		}
+		for (unsigned i = 0; i < 2; ++i) {
+			asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(
+							 reinterpret_cast<unsigned long long>(slot[i].b))
+						 : "memory");
+		}
+	}
+	__syncthreads();
+
+	GemmParams p{};
+	p.m = static_cast<u32>(a_rows);
+	p.n_raw = X17_N_RAW;
+	p.k = X17_K;
+	p.k_a = X17_K;
+	p.tiles_m = (p.m + gemm_cfg::BM - 1) / gemm_cfg::BM;
+	p.tiles_n = (X17_N_RAW + gemm_cfg::BN - 1) / gemm_cfg::BN;
+	p.c = c;
+	p.c_stride = X17_C_STRIDE;
+	p.resid_stride = X17_RESID_STRIDE;
+	p.head_dim = X17_HEAD_DIM;
+	p.rrms_cols = X17_RRMS_COLS;
+	p.k0 = __uint_as_float(X17_K0);
+	p.k1 = __uint_as_float(X17_K1);
+	p.k2 = __uint_as_float(X17_K2);
+	p.k3 = __uint_as_float(X17_K3);
+	p.k4 = __uint_as_float(X17_K4);
+	p.status = g_status;
+#if X17_EPI == 1
+	p.rrms = rrms;
+#endif
+#if X17_EPI == 3 || X17_EPI == 4
+	p.residual = residual;
+#endif
+	gemm_body<X17_EPI, false>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
+							  reinterpret_cast<CUtensorMap const *>(slot[1].b), p);
+}

@@ -4,8 +4,9 @@ The reference's host renders a template per shape, compiles it with nvcc into a 
 `extern "C" kernel(...)`, runs a small program that prints launch metadata as JSON, loads the cubin
 through the shim and launches it with an array of pointers to the arguments
 (src/device/cuda/kernel_build.rs:38-134, cuda_shim.rs:464-489).  This module does the same for the
-kernel of this path that needs no host-encoded TMA descriptor (RMSNorm); the tensor-core kernels take
-their tensor maps from the host and are reached through their own entry points instead.
+RMSNorm kernel and for the int8 x int8 GEMMs; the GEMM objects carry templates of their TMA tensor maps
+and finish them on the device with the pointers they are launched with. The attention kernel is reached
+through its entry point.
 """
 import ctypes
 import json
@@ -43,6 +44,45 @@ def build_rms_norm(model_dim: int, eps: float = 2.0 ** -70, force: bool = False)
         raise X17Error(f"nvcc failed for {src}:\n{res.stderr}")
     meta.write_text(json.dumps({"THREADS_PER_BLOCK": THREADS_PER_BLOCK, "SMEM_BYTES": 0, "ROWS_PER_BLOCK": ROWS_PER_BLOCK},
                                indent="\t") + "\n")
+    return d
+
+
+def build_gemm(config, name: str, force: bool = False) -> Path:
+    """One int8 x int8 GEMM configuration (a kernels.GemmConfig) as cache/kernels/<name>/kernel.cubin +
+    meta.json, the form GemmKernel::new produces in the reference (gemm.rs:368-443): the epilogue
+    constants and templates of the two TMA tensor maps come from x17ai_b200_gemm_object_desc (the maps
+    need the CUDA driver, so this runs where a GPU is), the kernel patches the maps with the pointers
+    and row count it is launched with. Launch it as the reference does: grid
+    (c_rows / M_PER_BLOCK, raw_cols / N_PER_BLOCK, 1), arguments (a, a_rows, b, b_rows, c[, rrms][, residual])."""
+    d = CACHE / name
+    cubin, meta = d / "kernel.cubin", d / "meta.json"
+    src = SRC / "gemm.cu"
+    newest = max(f.stat().st_mtime for f in (src, SRC.parent / "gemm.cuh", SRC.parent / "ptx.cuh"))
+    desc = _lib.GemmObjectDesc()
+    cfg = config._c()
+    check(_lib.load().x17ai_b200_gemm_object_desc(ctypes.byref(cfg), ctypes.byref(desc)))
+    fields = ("epilogue_kind", "n_raw", "k", "head_dim", "rrms_cols", "c_stride", "resid_stride", "k0", "k1", "k2", "k3", "k4")
+    key = json.dumps([int(getattr(desc, f)) for f in fields] + list(desc.map_a) + list(desc.map_b))
+    stamp = d / "config.json"
+    if (not force and cubin.exists() and meta.exists() and stamp.exists() and stamp.read_text() == key
+            and cubin.stat().st_mtime >= newest):
+        return d
+    d.mkdir(parents=True, exist_ok=True)
+    maps = d / "maps.h"
+    maps.write_text("#define X17_MAP_A " + ",".join(str(v) for v in desc.map_a) + "\n"
+                    "#define X17_MAP_B " + ",".join(str(v) for v in desc.map_b) + "\n")
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    defs = {"X17_EPI": desc.epilogue_kind, "X17_N_RAW": desc.n_raw, "X17_K": desc.k, "X17_HEAD_DIM": desc.head_dim,
+            "X17_RRMS_COLS": desc.rrms_cols, "X17_C_STRIDE": desc.c_stride, "X17_RESID_STRIDE": desc.resid_stride,
+            "X17_K0": desc.k0, "X17_K1": desc.k1, "X17_K2": desc.k2, "X17_K3": desc.k3, "X17_K4": desc.k4}
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--ftz=true", "--fmad=true",
+           "-include", str(maps)] + [f"-D{k}={int(v)}u" for k, v in defs.items()] + ["--cubin", "-o", str(cubin), str(src)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise X17Error(f"nvcc failed for {src}:\n{res.stderr}")
+    meta.write_text(json.dumps({"THREADS_PER_BLOCK": int(desc.threads), "SMEM_BYTES": int(desc.smem_bytes),
+                                "M_PER_BLOCK": int(desc.m_per_block), "N_PER_BLOCK": int(desc.n_per_block)}, indent="\t") + "\n")
+    stamp.write_text(key)
     return d
 
 
