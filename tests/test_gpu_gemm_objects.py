@@ -94,3 +94,96 @@ def test_gemm_object_any_grid_and_reuse(stream):
     _launch_object(stream, cfg, "any_grid", a2, b, got2, grid=(2, 4, 1))
     stream.synchronize()
     assert torch.equal(got2, want2)
+
+
+def _launch_attn_object(stream, kern, S, H, tq, tkv, tsk, tsv, tt, out, l, window):
+    m = kern.meta
+    p = lambda x: ctypes.c_void_p(x.data_ptr() if x is not None else 0)
+    kern.launch(stream, (S // m["Q_PER_BLOCK"], H, 1), (m["THREADS_PER_BLOCK"], 1, 1), m["SMEM_BYTES"],
+                ctypes.c_uint64(S), p(tq), p(tkv), p(tsk), p(tsv), p(tt), p(out), p(l), ctypes.c_uint64(window))
+
+
+@pytest.mark.parametrize("name,S2,W2", [("block_d128_w128", 1024, 256)])
+def test_attention_object(stream, name, S2, W2):
+    """The attention kernel object, launched with the reference's grid and argument list (attn.rs:412-447):
+    the bytes of the entry point on the fixture, then again with other buffers, another sequence length and
+    window (the maps are patched at every launch), and with a null `l`."""
+    from x17ai_b200 import kernel_objects, kernels as K
+    g, c = load_golden(name)
+    S, D, H, W = c["S"], c["D"], c["H"], c["W"]
+    cfg = K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D)
+    kern = kernel_objects.CubinKernel(stream, kernel_objects.build_attn(cfg, f"attn_{name}"))
+    lib = K.AttnKernel(cfg)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    sk, sv, tt = t(g["sinks_k_i8"].reshape(H, D)), t(g["sinks_v_i8"].reshape(H, D)), t(g["attn_temperature_f32"].reshape(H))
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    codes = lambda *s: torch.clamp(torch.round(torch.randn(*s, generator=gen, device="cuda") * 8.0), -127, 127).to(torch.int8)
+    cases = [(S, W, t(g["q_i8"].reshape(S, H * D)), t(g["kv_i8"].reshape(S, 2 * H * D))),
+             (S2, W2, codes(S2, H * D), codes(S2, 2 * H * D)),
+             (S2, 0, codes(S2, H * D), codes(S2, 2 * H * D))]
+    for s_len, win, q, kv in cases:
+        out_o = torch.zeros(s_len, H * D, dtype=torch.int8, device="cuda")
+        out_l = torch.zeros(s_len, H * D, dtype=torch.int8, device="cuda")
+        l_o = torch.zeros(H, s_len, dtype=torch.float32, device="cuda")
+        l_l = torch.zeros(H, s_len, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        _launch_attn_object(stream, kern, s_len, H, q, kv, sk, sv, tt, out_o, l_o, win)
+        lib.launch(stream, q, kv, sk, sv, tt, out_l, l_l, win)
+        stream.synchronize()
+        assert torch.equal(out_o, out_l) and torch.equal(l_o, l_l), (s_len, win)
+        out_n = torch.zeros_like(out_o)
+        torch.cuda.synchronize()
+        _launch_attn_object(stream, kern, s_len, H, q, kv, sk, sv, tt, out_n, None, win)
+        stream.synchronize()
+        assert torch.equal(out_n, out_l)
+    kern.unload()
+
+
+def test_objects_in_the_reference_harness_shape(stream):
+    """One sequence of the benchmark's shape through the attention object and the Q projection object with
+    the reference's grids: same bytes as the entry points, and the device times next to them."""
+    from x17ai_b200 import device, kernel_objects, kernels as K
+    H, D, S, W, Dm = 32, 128, 8192, 1024, 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    codes = lambda *s: torch.clamp(torch.round(torch.randn(*s, generator=gen, device="cuda") * 8.0), -127, 127).to(torch.int8)
+    x, wq = codes(S, Dm), codes(H * D, Dm)
+    q, kv, sk, sv = codes(S, H * D), codes(S, 2 * H * D), codes(H, D), codes(H, D)
+    tt = (0.5 + torch.rand(H, generator=gen, device="cuda")).float()
+    acfg = K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D)
+    gcfg = K.attn_q_fwd_config(Dm, H * D)
+    a_obj = kernel_objects.CubinKernel(stream, kernel_objects.build_attn(acfg, "attn_h32_d128"))
+    g_obj = kernel_objects.CubinKernel(stream, kernel_objects.build_gemm(gcfg, "attn_q_4096_4096"))
+    a_lib, g_lib = K.AttnKernel(acfg), K.GemmKernel(gcfg)
+    out_o, out_l = (torch.zeros(S, H * D, dtype=torch.int8, device="cuda") for _ in range(2))
+    q_o, q_l = (torch.zeros(S, H * D, dtype=torch.int8, device="cuda") for _ in range(2))
+    torch.cuda.synchronize()
+    p = lambda t_: ctypes.c_void_p(t_.data_ptr())
+    gm = g_obj.meta
+
+    def run_g_obj():
+        g_obj.launch(stream, (S // gm["M_PER_BLOCK"], (H * D) // gm["N_PER_BLOCK"], 1), (gm["THREADS_PER_BLOCK"], 1, 1),
+                     gm["SMEM_BYTES"], p(x), ctypes.c_uint64(S), p(wq), ctypes.c_uint64(H * D), p(q_o))
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        tm = device.CudaTimer(stream)
+        tm.start()
+        for _ in range(n):
+            fn()
+        tm.stop()
+        stream.synchronize()
+        s = tm.elapsed_seconds() / n
+        tm.destroy()
+        return s
+
+    t_ao = timed(lambda: _launch_attn_object(stream, a_obj, S, H, q, kv, sk, sv, tt, out_o, None, W))
+    t_al = timed(lambda: a_lib.launch(stream, q, kv, sk, sv, tt, out_l, None, W))
+    t_go = timed(run_g_obj)
+    t_gl = timed(lambda: g_lib.launch(stream, x, wq, q_l))
+    print(f"attention: object {t_ao * 1e3:.3f} ms, entry point {t_al * 1e3:.3f} ms; "
+          f"Q projection: object {t_go * 1e3:.3f} ms, entry point {t_gl * 1e3:.3f} ms")
+    assert torch.equal(out_o, out_l) and torch.equal(q_o, q_l)
+    assert t_ao < 1.2 * t_al and t_go < 2.0 * t_gl
+    a_obj.unload()
+    g_obj.unload()

@@ -64,6 +64,11 @@ class GemmObjectDesc(Structure):
                 ("map_a", c_uint8 * 128), ("map_b", c_uint8 * 128)]
 
 
+class AttnObjectDesc(Structure):
+    _fields_ = [("smem_bytes", c_uint32), ("threads", c_uint32), ("q_per_block", c_uint32), ("reserved", c_uint32),
+                ("map_q", c_uint8 * 128), ("map_kv", c_uint8 * 128)]
+
+
 class QkvgConfig(Structure):
     _fields_ = [("model_dim", c_size_t), ("n_heads", c_size_t), ("head_dim", c_size_t), ("gate_cols", c_size_t),
                 ("inp_scale", c_double), ("out_scale", c_double), ("eps", c_double)]
@@ -121,6 +126,7 @@ SIGNATURES = {
     "x17ai_b200_graph_launch": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_destroy": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_kernel_nodes": (c_uint64, [c_void_p]),
+    "x17ai_b200_attn_object_desc": (DIAG, [POINTER(AttnConfig), POINTER(AttnObjectDesc)]),
     "x17ai_b200_gemm_object_desc": (DIAG, [POINTER(GemmConfig), POINTER(GemmObjectDesc)]),
     "x17ai_b200_launch_count": (c_uint64, []),
 }

@@ -484,6 +484,42 @@ int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
 }
 #endif
 
+x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_AttnConfig const *cfg, x17ai_AttnObjectDesc *desc) {
+	char const *who = "x17ai_b200_attn_object_desc()";
+	if (desc == nullptr) return static_diag("x17ai_b200_attn_object_desc(): null argument");
+	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (cfg->head_dim != 128) {
+		return make_diag("x17ai_b200: unsupported kernel object", who,
+						 ": the attention kernel object exists for head_dim 128 (the reference's host launches one CTA per "
+						 "128 / head_dim heads, this kernel takes one head per CTA)");
+	}
+	if (!x17::driver().ok) {
+		return make_diag("x17ai_b200: CUDA driver not available", who, ": the CUDA driver is not available on this machine (",
+						 x17::driver().missing, " not found)");
+	}
+	std::memset(desc, 0, sizeof(*desc));
+	uint32_t const d = uint32_t(cfg->head_dim);
+	desc->threads = x17::attn_cfg::THREADS;
+	desc->q_per_block = x17::attn_cfg::BQ;
+	uint32_t const smem = x17::attn_cfg::smem_bytes<128>();
+	desc->smem_bytes = smem < 80u * 1024u ? 80u * 1024u : smem;
+	void *const dummy = reinterpret_cast<void *>(uintptr_t(1) << 20);
+	size_t const rows = x17::attn_cfg::BQ;   // placeholder: the kernel object writes the sequence length
+	CUtensorMap tq, tkv;
+	CUresult e = make_map_3d(&tq, dummy, cfg->n_heads * d, rows, 1, cfg->q_stride, cfg->q_stride * rows, d, x17::attn_cfg::BQ);
+	if (e == CUDA_SUCCESS) {
+		e = make_map_3d(&tkv, dummy, 2 * cfg->n_heads * d, rows, 1, cfg->kv_stride, cfg->kv_stride * rows, d,
+						x17::attn_cfg::BKV);
+	}
+	if (e != CUDA_SUCCESS) {
+		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who, ": cuTensorMapEncodeTiled failed: ",
+						 x17::cu_error_text(e));
+	}
+	std::memcpy(desc->map_q, &tq, 128);
+	std::memcpy(desc->map_kv, &tkv, 128);
+	return nullptr;
+}
+
 x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg, x17ai_GemmObjectDesc *desc) {
 	char const *who = "x17ai_b200_gemm_object_desc()";
 	if (desc == nullptr) return static_diag("x17ai_b200_gemm_object_desc(): null argument");

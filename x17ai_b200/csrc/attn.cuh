@@ -171,10 +171,10 @@ __device__ unsigned g_ntimes[4];
 
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
 // accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
+// The tensor maps are reached through pointers: kernel parameters for the library's entry points, maps
+// patched on the device for the kernel object (kernel_objects/attn.cu).
 template <u32 D, bool DEBUG, bool FP8PV = false>
-__global__ void __launch_bounds__(attn_cfg::THREADS, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-				const AttnParams p) {
+X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv_ptr, AttnParams const &p) {
 	using namespace attn_cfg;
 	static_assert(D == 32 || D == 64 || D == 128, "head_dim must be 32, 64 or 128");
 	constexpr u32 TILE_BYTES = BKV * D;
@@ -250,10 +250,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 	if (warp == 0) {
 		// ---------------- TMA producer ----------------
 		if (elect_one()) {
-			tma_prefetch_desc(&tm_q);
-			tma_prefetch_desc(&tm_kv);
+			tma_prefetch_desc(tm_q_ptr);
+			tma_prefetch_desc(tm_kv_ptr);
 			mbar_expect_tx(q_full_bar, BQ * D);
-			tma_load_3d(s_q, &tm_q, q_full_bar, i32(head * D), i32(q0), i32(batch));
+			tma_load_3d(s_q, tm_q_ptr, q_full_bar, i32(head * D), i32(q0), i32(batch));
 			u32 it = 0;
 			bool ok = true;
 			// one ring entry: the K (item 0) or V (item 1) tile of KV tile t
@@ -262,7 +262,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 				u32 const ph = (it / STAGES) & 1;
 				if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, ST_WAIT_STAGE_EMPTY, s)) return false;
 				mbar_expect_tx(full_bar(s), TILE_BYTES);
-				tma_load_3d(s_ring + s * TILE_BYTES, &tm_kv, full_bar(s), i32(2 * head * D + item * D),
+				tma_load_3d(s_ring + s * TILE_BYTES, tm_kv_ptr, full_bar(s), i32(2 * head * D + item * D),
 							i32(t * BKV), i32(batch));
 				++it;
 				X17_T(0, 1);
@@ -651,6 +651,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 		tc_fence_after();
 		tmem_dealloc(tmem_base, TMEM_COLS);
 	}
+}
+
+template <u32 D, bool DEBUG, bool FP8PV = false>
+__global__ void __launch_bounds__(attn_cfg::THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+				const AttnParams p) {
+	attn_fwd_body<D, DEBUG, FP8PV>(&tm_q, &tm_kv, p);
 }
 
 }  // namespace x17

@@ -4,9 +4,9 @@ The reference's host renders a template per shape, compiles it with nvcc into a 
 `extern "C" kernel(...)`, runs a small program that prints launch metadata as JSON, loads the cubin
 through the shim and launches it with an array of pointers to the arguments
 (src/device/cuda/kernel_build.rs:38-134, cuda_shim.rs:464-489).  This module does the same for the
-RMSNorm kernel and for the int8 x int8 GEMMs; the GEMM objects carry templates of their TMA tensor maps
-and finish them on the device with the pointers they are launched with. The attention kernel is reached
-through its entry point.
+RMSNorm kernel, the int8 x int8 GEMMs and the int8 attention at head_dim 128; the tensor-core objects
+carry templates of their TMA tensor maps and finish them on the device with the pointers they are
+launched with.
 """
 import ctypes
 import json
@@ -82,6 +82,42 @@ def build_gemm(config, name: str, force: bool = False) -> Path:
         raise X17Error(f"nvcc failed for {src}:\n{res.stderr}")
     meta.write_text(json.dumps({"THREADS_PER_BLOCK": int(desc.threads), "SMEM_BYTES": int(desc.smem_bytes),
                                 "M_PER_BLOCK": int(desc.m_per_block), "N_PER_BLOCK": int(desc.n_per_block)}, indent="\t") + "\n")
+    stamp.write_text(key)
+    return d
+
+
+def build_attn(config, name: str, force: bool = False) -> Path:
+    """The int8 attention kernel for one configuration (a kernels.AttnKernelConfig with head_dim 128) as
+    cache/kernels/<name>/kernel.cubin + meta.json, the form AttnKernel::new produces in the reference
+    (attn.rs:300-351). Launch it as the reference does: grid (seq_len / Q_PER_BLOCK, n_heads, 1), arguments
+    (seq_len, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size), attn.rs:412-447."""
+    d = CACHE / name
+    cubin, meta = d / "kernel.cubin", d / "meta.json"
+    src = SRC / "attn.cu"
+    newest = max(f.stat().st_mtime for f in (src, SRC.parent / "attn.cuh", SRC.parent / "ptx.cuh"))
+    desc = _lib.AttnObjectDesc()
+    cfg = config._c()
+    check(_lib.load().x17ai_b200_attn_object_desc(ctypes.byref(cfg), ctypes.byref(desc)))
+    key = json.dumps([config.n_heads, config.head_dim, config.q_stride, config.kv_stride, config.o_stride]
+                     + list(desc.map_q) + list(desc.map_kv))
+    stamp = d / "config.json"
+    if (not force and cubin.exists() and meta.exists() and stamp.exists() and stamp.read_text() == key
+            and cubin.stat().st_mtime >= newest):
+        return d
+    d.mkdir(parents=True, exist_ok=True)
+    maps = d / "maps.h"
+    maps.write_text("#define X17_MAP_Q " + ",".join(str(v) for v in desc.map_q) + "\n"
+                    "#define X17_MAP_KV " + ",".join(str(v) for v in desc.map_kv) + "\n")
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    defs = {"X17_N_HEADS": config.n_heads, "X17_Q_STRIDE": config.q_stride, "X17_KV_STRIDE": config.kv_stride,
+            "X17_O_STRIDE": config.o_stride}
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--ftz=true", "--fmad=true",
+           "-include", str(maps)] + [f"-D{k}={int(v)}u" for k, v in defs.items()] + ["--cubin", "-o", str(cubin), str(src)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise X17Error(f"nvcc failed for {src}:\n{res.stderr}")
+    meta.write_text(json.dumps({"THREADS_PER_BLOCK": int(desc.threads), "SMEM_BYTES": int(desc.smem_bytes),
+                                "Q_PER_BLOCK": int(desc.q_per_block)}, indent="\t") + "\n")
     stamp.write_text(key)
     return d
 
