@@ -118,12 +118,11 @@ X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx
 
 // The kernel proper. The tensor maps are reached through pointers: kernel parameters for the library's
 // entry points, maps patched on the device for the kernel objects (kernel_objects/gemm.cu). The loop
-// strides over the tiles by the number of CTAs of the launch, whatever the grid's shape.
+// strides over the tiles by `n_ctas`, this CTA being number `cta` of them, whatever the grid's shape.
 template <int EPI, bool F8>
-X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr, GemmParams const &p) {
+X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr, GemmParams const &p, u32 cta,
+					   u32 n_ctas) {
 	using namespace gemm_cfg;
-	u32 const cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-	u32 const n_ctas = gridDim.x * gridDim.y * gridDim.z;
 	extern __shared__ u8 smem_raw[];
 	u32 const smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	u8 *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -470,7 +469,7 @@ template <int EPI, bool F8>
 __global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
 			const GemmParams p) {
-	gemm_body<EPI, F8>(&tm_a, &tm_b, p);
+	gemm_body<EPI, F8>(&tm_a, &tm_b, p, blockIdx.x, gridDim.x);
 }
 
 }  // namespace x17

@@ -55,6 +55,17 @@ kernel(void const *a, unsigned long long a_rows, void const *b, unsigned long lo
 	(void)b_rows;   // fixed at compile time (X17_N_RAW), as in the reference's templates
 	__shared__ MapBytes s_maps[2];
 
+	// The reference's grid has one CTA per output tile. One CTA per SM works through the tiles (the loop
+	// overlaps the epilogue of a tile with the main loop of the next); the CTAs beyond that leave at once.
+	u32 cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+	u32 n_ctas = gridDim.x * gridDim.y * gridDim.z;
+	unsigned n_sm;
+	asm volatile("mov.u32 %0, %%nsmid;" : "=r"(n_sm));
+	if (n_ctas > n_sm) {
+		if (cta >= n_sm) return;
+		n_ctas = n_sm;
+	}
+
 	unsigned smid;
 	asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
 	MapBytes *const slot = g_maps[smid & 255u];
@@ -111,5 +122,5 @@ kernel(void const *a, unsigned long long a_rows, void const *b, unsigned long lo
 	p.residual = residual;
 #endif
 	gemm_body<X17_EPI, false>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
-							  reinterpret_cast<CUtensorMap const *>(slot[1].b), p);
+							  reinterpret_cast<CUtensorMap const *>(slot[1].b), p, cta, n_ctas);
 }
