@@ -360,17 +360,19 @@ typedef struct x17ai_GemmObjectDesc {
 	uint32_t smem_bytes, threads, m_per_block, n_per_block;
 	uint8_t map_a[128], map_b[128];
 } x17ai_GemmObjectDesc;
-x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg, x17ai_GemmObjectDesc *desc);
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
+                                                    x17ai_GemmObjectDesc *desc);
 
 /* The same for the attention kernel object (templates/attn/kernel.cu:9-20, attn.rs:336-447): launch
- * metadata and templates of the Q and KV tensor maps for one configuration (head_dim 128: one head per
- * CTA, as the reference's own grid has it for that width); the kernel object writes the base
- * addresses and the sequence length on the device. */
+ * metadata and templates of the Q and KV tensor maps for one configuration; the kernel object writes
+ * the base addresses and the sequence length on the device and, under the reference's grid of one CTA
+ * per 128 / head_dim heads, goes through the heads of its group one after the other. */
 typedef struct x17ai_AttnObjectDesc {
 	uint32_t smem_bytes, threads, q_per_block, reserved;
 	uint8_t map_q[128], map_kv[128];
 } x17ai_AttnObjectDesc;
-x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_AttnConfig const *cfg, x17ai_AttnObjectDesc *desc);
+x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg,
+                                                    x17ai_AttnObjectDesc *desc);
 
 /* Device-side status of the kernels launched so far on the stream's device: synchronises the
  * stream, copies the four status words (0 = ok; else code << 16 | detail of the first bounded

@@ -126,8 +126,8 @@ SIGNATURES = {
     "x17ai_b200_graph_launch": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_destroy": (DIAG, [c_void_p, c_void_p]),
     "x17ai_b200_graph_kernel_nodes": (c_uint64, [c_void_p]),
-    "x17ai_b200_attn_object_desc": (DIAG, [POINTER(AttnConfig), POINTER(AttnObjectDesc)]),
-    "x17ai_b200_gemm_object_desc": (DIAG, [POINTER(GemmConfig), POINTER(GemmObjectDesc)]),
+    "x17ai_b200_attn_object_desc": (DIAG, [c_void_p, POINTER(AttnConfig), POINTER(AttnObjectDesc)]),
+    "x17ai_b200_gemm_object_desc": (DIAG, [c_void_p, POINTER(GemmConfig), POINTER(GemmObjectDesc)]),
     "x17ai_b200_launch_count": (c_uint64, []),
 }
 

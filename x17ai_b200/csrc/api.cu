@@ -484,24 +484,20 @@ int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
 }
 #endif
 
-x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_AttnConfig const *cfg, x17ai_AttnObjectDesc *desc) {
+x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg,
+													x17ai_AttnObjectDesc *desc) {
 	char const *who = "x17ai_b200_attn_object_desc()";
 	if (desc == nullptr) return static_diag("x17ai_b200_attn_object_desc(): null argument");
 	if (auto *d = check_attn_config(cfg, who)) return d;
-	if (cfg->head_dim != 128) {
-		return make_diag("x17ai_b200: unsupported kernel object", who,
-						 ": the attention kernel object exists for head_dim 128 (the reference's host launches one CTA per "
-						 "128 / head_dim heads, this kernel takes one head per CTA)");
-	}
-	if (!x17::driver().ok) {
-		return make_diag("x17ai_b200: CUDA driver not available", who, ": the CUDA driver is not available on this machine (",
-						 x17::driver().missing, " not found)");
-	}
+	StreamScope scope(stream, who);   // the driver encodes tensor maps inside a context
+	if (scope.diag) return scope.diag;
 	std::memset(desc, 0, sizeof(*desc));
 	uint32_t const d = uint32_t(cfg->head_dim);
 	desc->threads = x17::attn_cfg::THREADS;
 	desc->q_per_block = x17::attn_cfg::BQ;
-	uint32_t const smem = x17::attn_cfg::smem_bytes<128>();
+	uint32_t const smem = d == 128 ? x17::attn_cfg::smem_bytes<128>()
+						  : d == 64 ? x17::attn_cfg::smem_bytes<64>()
+									: x17::attn_cfg::smem_bytes<32>();
 	desc->smem_bytes = smem < 80u * 1024u ? 80u * 1024u : smem;
 	void *const dummy = reinterpret_cast<void *>(uintptr_t(1) << 20);
 	size_t const rows = x17::attn_cfg::BQ;   // placeholder: the kernel object writes the sequence length
@@ -520,7 +516,8 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_AttnConfig const *cfg,
 	return nullptr;
 }
 
-x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg, x17ai_GemmObjectDesc *desc) {
+x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
+													x17ai_GemmObjectDesc *desc) {
 	char const *who = "x17ai_b200_gemm_object_desc()";
 	if (desc == nullptr) return static_diag("x17ai_b200_gemm_object_desc(): null argument");
 	GemmPlan plan{};
@@ -529,10 +526,8 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_GemmConfig const *cfg,
 		return make_diag("x17ai_b200: unsupported kernel object", who,
 						 ": kernel objects exist for int8 x int8 GEMMs (the split e4m3 weight planes are not what the reference's host passes)");
 	}
-	if (!x17::driver().ok) {
-		return make_diag("x17ai_b200: CUDA driver not available", who, ": the CUDA driver is not available on this machine (",
-						 x17::driver().missing, " not found)");
-	}
+	StreamScope scope(stream, who);   // the driver encodes tensor maps inside a context
+	if (scope.diag) return scope.diag;
 	using namespace x17::gemm_cfg;
 	x17::GemmParams p{};
 	fill_gemm_params(cfg, plan, BM, p);

@@ -172,9 +172,13 @@ __device__ unsigned g_ntimes[4];
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
 // accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
 // The tensor maps are reached through pointers: kernel parameters for the library's entry points, maps
-// patched on the device for the kernel object (kernel_objects/attn.cu).
+// patched on the device for the kernel object (kernel_objects/attn.cu). `head` is the head this call
+// works on; the body may be called again by the same CTA for another head (it invalidates its
+// barriers and frees its TMEM columns before it returns) provided `more_calls` was set on the earlier
+// calls: a CTA that has given up its TMEM allocation permit must not allocate again.
 template <u32 D, bool DEBUG, bool FP8PV = false>
-X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv_ptr, AttnParams const &p) {
+X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv_ptr, AttnParams const &p, u32 head,
+						   bool more_calls = false) {
 	using namespace attn_cfg;
 	static_assert(D == 32 || D == 64 || D == 128, "head_dim must be 32, 64 or 128");
 	constexpr u32 TILE_BYTES = BKV * D;
@@ -213,7 +217,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 
 	// heavier query tiles (more visible keys) first
 	u32 const q_tile = gridDim.x - 1 - blockIdx.x;
-	u32 const head = blockIdx.y;
 	u32 const batch = blockIdx.z;
 	u32 const q0 = q_tile * BQ;
 	u32 const w = p.window;
@@ -240,7 +243,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 	}
 	if (warp == 1) {
 		tmem_alloc(tmem_slot, TMEM_COLS);
-		tmem_relinquish();
+		if (!more_calls) tmem_relinquish();
 	}
 	tc_fence_before();
 	__syncthreads();
@@ -651,13 +654,17 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		tc_fence_after();
 		tmem_dealloc(tmem_base, TMEM_COLS);
 	}
+	if (threadIdx.x == 0) {
+		// every phase has completed: the barrier words may be initialised again by a later call
+		for (u32 i = 0; i < 2 * STAGES + 8; ++i) mbar_inval(bar_base + 8 * i);
+	}
 }
 
 template <u32 D, bool DEBUG, bool FP8PV = false>
 __global__ void __launch_bounds__(attn_cfg::THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
 				const AttnParams p) {
-	attn_fwd_body<D, DEBUG, FP8PV>(&tm_q, &tm_kv, p);
+	attn_fwd_body<D, DEBUG, FP8PV>(&tm_q, &tm_kv, p, blockIdx.y);
 }
 
 }  // namespace x17

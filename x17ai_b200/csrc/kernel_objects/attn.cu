@@ -2,15 +2,16 @@
 //   extern "C" kernel(usize seq_len, i8 *q, i8 *kv, const i8 *sink_k, const i8 *sink_v,
 //                     const f32 *attn_temperature, i8 *out, f32 *l /*nullable*/, usize window_size)
 // with heads, head_dim and the row strides fixed at compile time, launched by the reference's host with
-// its own grid (seq_len / Q_PER_BLOCK, n_heads / max(128 / head_dim, 1), 1), attn.rs:425-447. head_dim is
-// 128 here, so that grid has one CTA per (query tile, head), which is this kernel's own decomposition.
+// its own grid (seq_len / Q_PER_BLOCK, n_heads / max(128 / head_dim, 1), 1), attn.rs:425-447: one CTA per
+// query tile and group of 128 / head_dim heads. This kernel works on one head at a time, so a CTA
+// goes through the heads of its group one after the other.
 //
 // As in kernel_objects/gemm.cu the two TMA tensor maps are baked in as templates (X17_MAP_Q, X17_MAP_KV)
 // and finished on the device: base addresses and the sequence length are written with tensormap.replace
 // and the maps are published to a slot in global memory. Two CTAs share an SM, so each SM owns a small
 // ring of slots handed out by a counter; every CTA of a launch writes the same bytes.
 //
-// Compile with -DX17_N_HEADS= -DX17_Q_STRIDE= -DX17_KV_STRIDE= -DX17_O_STRIDE= and -include a header
+// Compile with -DX17_HEAD_DIM= -DX17_N_HEADS= -DX17_Q_STRIDE= -DX17_KV_STRIDE= -DX17_O_STRIDE= and -include a header
 // defining X17_MAP_Q and X17_MAP_KV.
 #include "../attn.cuh"
 
@@ -105,6 +106,13 @@ kernel(unsigned long long seq_len, signed char const *q, signed char const *kv, 
 	p.l = l;
 	p.l_batch_stride = 0;
 	p.status = g_status;
-	attn_fwd_body<128, false, false>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
-									 reinterpret_cast<CUtensorMap const *>(slot[1].b), p);
+	constexpr u32 HEADS_PER_CTA = X17_HEAD_DIM >= 128 ? 1 : 128 / X17_HEAD_DIM;
+	for (u32 h = 0; h < HEADS_PER_CTA; ++h) {
+		u32 const head = blockIdx.y * HEADS_PER_CTA + h;
+		if (head >= X17_N_HEADS) break;
+		attn_fwd_body<X17_HEAD_DIM, false, false>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
+												  reinterpret_cast<CUtensorMap const *>(slot[1].b), p, head,
+												  h + 1 < HEADS_PER_CTA);
+		__syncthreads();
+	}
 }

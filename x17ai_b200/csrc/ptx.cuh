@@ -139,6 +139,9 @@ X17_DEV u64 add_f32x2(u64 a, u64 b) {
 X17_DEV void mbar_init(u32 bar, u32 count) {
 	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+X17_DEV void mbar_inval(u32 bar) {
+	asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 X17_DEV void mbar_fence_init() {
 	asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

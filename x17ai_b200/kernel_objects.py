@@ -4,7 +4,7 @@ The reference's host renders a template per shape, compiles it with nvcc into a 
 `extern "C" kernel(...)`, runs a small program that prints launch metadata as JSON, loads the cubin
 through the shim and launches it with an array of pointers to the arguments
 (src/device/cuda/kernel_build.rs:38-134, cuda_shim.rs:464-489).  This module does the same for the
-RMSNorm kernel, the int8 x int8 GEMMs and the int8 attention at head_dim 128; the tensor-core objects
+RMSNorm kernel, the int8 x int8 GEMMs and the int8 attention; the tensor-core objects
 carry templates of their TMA tensor maps and finish them on the device with the pointers they are
 launched with.
 """
@@ -47,7 +47,7 @@ def build_rms_norm(model_dim: int, eps: float = 2.0 ** -70, force: bool = False)
     return d
 
 
-def build_gemm(config, name: str, force: bool = False) -> Path:
+def build_gemm(stream, config, name: str, force: bool = False) -> Path:
     """One int8 x int8 GEMM configuration (a kernels.GemmConfig) as cache/kernels/<name>/kernel.cubin +
     meta.json, the form GemmKernel::new produces in the reference (gemm.rs:368-443): the epilogue
     constants and templates of the two TMA tensor maps come from x17ai_b200_gemm_object_desc (the maps
@@ -60,7 +60,7 @@ def build_gemm(config, name: str, force: bool = False) -> Path:
     newest = max(f.stat().st_mtime for f in (src, SRC.parent / "gemm.cuh", SRC.parent / "ptx.cuh"))
     desc = _lib.GemmObjectDesc()
     cfg = config._c()
-    check(_lib.load().x17ai_b200_gemm_object_desc(ctypes.byref(cfg), ctypes.byref(desc)))
+    check(_lib.load().x17ai_b200_gemm_object_desc(stream.handle, ctypes.byref(cfg), ctypes.byref(desc)))
     fields = ("epilogue_kind", "n_raw", "k", "head_dim", "rrms_cols", "c_stride", "resid_stride", "k0", "k1", "k2", "k3", "k4")
     key = json.dumps([int(getattr(desc, f)) for f in fields] + list(desc.map_a) + list(desc.map_b))
     stamp = d / "config.json"
@@ -86,10 +86,11 @@ def build_gemm(config, name: str, force: bool = False) -> Path:
     return d
 
 
-def build_attn(config, name: str, force: bool = False) -> Path:
-    """The int8 attention kernel for one configuration (a kernels.AttnKernelConfig with head_dim 128) as
+def build_attn(stream, config, name: str, force: bool = False) -> Path:
+    """The int8 attention kernel for one configuration (a kernels.AttnKernelConfig) as
     cache/kernels/<name>/kernel.cubin + meta.json, the form AttnKernel::new produces in the reference
-    (attn.rs:300-351). Launch it as the reference does: grid (seq_len / Q_PER_BLOCK, n_heads, 1), arguments
+    (attn.rs:300-351). Launch it as the reference does: grid
+    (seq_len / Q_PER_BLOCK, n_heads / max(128 / head_dim, 1), 1), arguments
     (seq_len, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size), attn.rs:412-447."""
     d = CACHE / name
     cubin, meta = d / "kernel.cubin", d / "meta.json"
@@ -97,7 +98,7 @@ def build_attn(config, name: str, force: bool = False) -> Path:
     newest = max(f.stat().st_mtime for f in (src, SRC.parent / "attn.cuh", SRC.parent / "ptx.cuh"))
     desc = _lib.AttnObjectDesc()
     cfg = config._c()
-    check(_lib.load().x17ai_b200_attn_object_desc(ctypes.byref(cfg), ctypes.byref(desc)))
+    check(_lib.load().x17ai_b200_attn_object_desc(stream.handle, ctypes.byref(cfg), ctypes.byref(desc)))
     key = json.dumps([config.n_heads, config.head_dim, config.q_stride, config.kv_stride, config.o_stride]
                      + list(desc.map_q) + list(desc.map_kv))
     stamp = d / "config.json"
@@ -109,7 +110,7 @@ def build_attn(config, name: str, force: bool = False) -> Path:
     maps.write_text("#define X17_MAP_Q " + ",".join(str(v) for v in desc.map_q) + "\n"
                     "#define X17_MAP_KV " + ",".join(str(v) for v in desc.map_kv) + "\n")
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    defs = {"X17_N_HEADS": config.n_heads, "X17_Q_STRIDE": config.q_stride, "X17_KV_STRIDE": config.kv_stride,
+    defs = {"X17_HEAD_DIM": config.head_dim, "X17_N_HEADS": config.n_heads, "X17_Q_STRIDE": config.q_stride, "X17_KV_STRIDE": config.kv_stride,
             "X17_O_STRIDE": config.o_stride}
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--ftz=true", "--fmad=true",
            "-include", str(maps)] + [f"-D{k}={int(v)}u" for k, v in defs.items()] + ["--cubin", "-o", str(cubin), str(src)]
