@@ -154,18 +154,20 @@ def test_faster_than_the_reference_kernel(stream):
     def run_ours():
         ours.launch(stream, q, kv, sk, sv, temp, out, l, W)
 
-    def timed(fn, n=10):
+    def timed(fn, n=11):
+        """Median device time of single launches (a timer around each: host pauses between launches do not count)."""
         for _ in range(3):
             fn()
-        t = device.CudaTimer(stream)
-        t.start()
-        for _ in range(n):
+        timers = [device.CudaTimer(stream) for _ in range(n)]
+        for t in timers:
+            t.start()
             fn()
-        t.stop()
+            t.stop()
         stream.synchronize()
-        s = t.elapsed_seconds() / n
-        t.destroy()
-        return s
+        times = sorted(t.elapsed_seconds() for t in timers)
+        for t in timers:
+            t.destroy()
+        return times[n // 2]
 
     t_ref, t_ours = timed(run_ref), timed(run_ours)
     ops = o_attn.attn_ops(1, H, D, S, W)
