@@ -223,3 +223,22 @@ def test_layer_sequential_form(stream, name):
         assert (got["ffn_y"] != ref).mean() <= 2e-3
         h = out["ffn_y"].clone()   # the next layer's hidden state
         torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("name", ["block_d64_w64", "block_d128_w128", "block_d32_w0"])
+def test_block_through_kernel_objects(stream, name):
+    """The block with its kernels loaded as kernel objects (kernel.cubin + meta.json through the generic shim
+    calls, the reference's grids and argument lists) returns the bytes of the block on the entry points."""
+    from x17ai_b200.block import BlockConfig, BlockForward
+    g, c = load_golden(name)
+    S, Dm, D, H, F, W = c["S"], c["Dm"], c["D"], c["H"], c["F"], c["W"]
+    plain, x = _block(stream, g, c, False)
+    want = {k: v.clone() for k, v in plain.forward(x).items()}
+    stream.synchronize()
+    obj = BlockForward(stream, BlockConfig(Dm, H, D, F, W), plain.w_q, plain.w_kv, plain.w_attn_y, plain.w_ffn_f, plain.w_ffn_y,
+                       plain.sink_k, plain.sink_v, plain.attn_temperature, kernel_objects=True)
+    got = obj.forward(x, timed=True)
+    stream.synchronize()
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+    assert np.array_equal(got["q"].cpu().numpy(), g["q_i8"].reshape(S, H * D))

@@ -45,7 +45,7 @@ class BlockForward:
     STAGES = ("attn_q", "attn_kv", "attn", "attn_y", "ffn_f", "ffn_y")
 
     def __init__(self, stream, config: BlockConfig, w_q, w_kv, w_attn_y, w_ffn_f, w_ffn_y, sink_k, sink_v,
-                 attn_temperature, fused_qkv: bool = False):
+                 attn_temperature, fused_qkv: bool = False, kernel_objects: bool = False):
         c = self.config = config
         self.stream = stream
         self.fused_qkv = fused_qkv
@@ -60,6 +60,19 @@ class BlockForward:
         self.k_attn_y = K.GemmKernel(K.attn_y_fwd_config(hd, c.model_dim))
         self.k_ffn_f = K.GemmKernel(K.ffn_f_fwd_config(c.model_dim, c.ffn_width))
         self.k_ffn_y = K.GemmKernel(K.ffn_y_fwd_f8_config(c.ffn_width, c.model_dim))
+        if kernel_objects:
+            # the five kernels that exist as kernel objects (kernel.cubin + meta.json, launched through the
+            # generic load_module / get_kernel / launch_kernel with the reference's grids and arguments)
+            # in place of the library's entry points; the e4m3 x int8 projection has no object
+            if fused_qkv:
+                raise K.X17Error("kernel_objects and fused_qkv exclude each other (the fused projection has no kernel object)")
+            from . import kernel_objects as KO
+            tag = f"{c.model_dim}_{c.n_heads}x{c.head_dim}_{c.ffn_width}"
+            self.k_q = KO.GemmObject(stream, self.k_q.config, f"attn_q_{tag}")
+            self.k_kv = KO.GemmObject(stream, self.k_kv.config, f"attn_kv_{tag}")
+            self.k_attn_y = KO.GemmObject(stream, self.k_attn_y.config, f"attn_y_{tag}")
+            self.k_ffn_f = KO.GemmObject(stream, self.k_ffn_f.config, f"ffn_f_{tag}")
+            self.k_attn = KO.AttnObject(stream, self.k_attn.config, f"attn_{tag}")
         # e4m3 activations x int8 weights run on the fp8 tensor path with the weights split once
         self.w_ffn_y_split = K.split_i8_weights(stream, w_ffn_y)
         if fused_qkv:
@@ -76,7 +89,8 @@ class BlockForward:
              "sink_v": "sinks_v_i8", "attn_temperature": "attn_temperature_f32"}
 
     @classmethod
-    def from_directory(cls, stream, directory, n_heads: int, head_dim: int, window_size: int, fused_qkv: bool = False):
+    def from_directory(cls, stream, directory, n_heads: int, head_dim: int, window_size: int, fused_qkv: bool = False,
+                       kernel_objects: bool = False):
         """Builds the block from the safetensors files the reference's harness reads (one tensor per
         file, `<name>.safetensors`), inferring model_dim and the FFN width from the weight shapes with
         the checks of validate_*_inputs (src/main.rs:257-385). Returns (block, x) with the input
@@ -99,7 +113,7 @@ class BlockForward:
         w_ffn_y = t["w_ffn_y"].reshape(2 * model_dim, ffn_width)
         blk = cls(stream, BlockConfig(model_dim, n_heads, head_dim, ffn_width, window_size), w_q, w_kv, w_attn_y, w_ffn_f,
                   w_ffn_y, t["sink_k"].reshape(n_heads, head_dim), t["sink_v"].reshape(n_heads, head_dim),
-                  t["attn_temperature"].reshape(n_heads), fused_qkv=fused_qkv)
+                  t["attn_temperature"].reshape(n_heads), fused_qkv=fused_qkv, kernel_objects=kernel_objects)
         x_path = d / "x_i8.safetensors"
         x = tensor_io.load_to_device(x_path, stream).reshape(-1, model_dim) if x_path.exists() else None
         return blk, x

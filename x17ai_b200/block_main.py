@@ -24,12 +24,13 @@ REPORT_NAMES = {"attn_q": "attn_q_fwd", "attn_kv": "attn_kv_fwd", "attn": "attn_
 
 
 def run(tensor_dir, output_dir, n_heads: int, head_dim: int, window_size: int, fused_qkv: bool = False,
-        device_id: int = 0, out=sys.stdout) -> dict:
+        device_id: int = 0, out=sys.stdout, kernel_objects: bool = False) -> dict:
     """Runs the harness once; returns {stage: seconds}."""
     import torch
     torch.cuda.set_device(device_id)
     with CudaStream(device_id) as stream:
-        blk, x = BlockForward.from_directory(stream, tensor_dir, n_heads, head_dim, window_size, fused_qkv=fused_qkv)
+        blk, x = BlockForward.from_directory(stream, tensor_dir, n_heads, head_dim, window_size, fused_qkv=fused_qkv,
+                                             kernel_objects=kernel_objects)
         if x is None:
             raise X17Error(f"{Path(tensor_dir) / 'x_i8.safetensors'} not found")
         result = blk.forward(x, timed=True)
@@ -69,10 +70,13 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, required=True)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--fused-qkv", action="store_true")
+    ap.add_argument("--kernel-objects", action="store_true",
+                    help="launch kernel.cubin + meta.json objects through load_module / get_kernel / launch_kernel, as the "
+                         "reference's host does with its own kernels (all stages but the e4m3 x int8 projection)")
     ap.add_argument("--device", type=int, default=0)
     a = ap.parse_args(argv)
     try:
-        run(a.tensor_dir, a.output_dir, a.heads, a.head_dim, a.window, a.fused_qkv, a.device)
+        run(a.tensor_dir, a.output_dir, a.heads, a.head_dim, a.window, a.fused_qkv, a.device, kernel_objects=a.kernel_objects)
     except X17Error as e:
         print(f"error: {e}", file=sys.stderr)
         return 1

@@ -143,3 +143,43 @@ class CubinKernel:
 
     def unload(self):
         check(self._lib.x17ai_cuda_del_module(self.module))
+
+
+class GemmObject:
+    """A GEMM kernel object with GemmKernel's launch interface: built once for its configuration, launched
+    through the generic shim calls with the reference's grid and argument list (gemm.rs:591-641)."""
+
+    def __init__(self, stream, config, name: str):
+        self.config = config
+        self.kernel = CubinKernel(stream, build_gemm(stream, config, name))
+
+    def launch(self, stream, a, b, c, rrms=None, residual=None):
+        m = self.kernel.meta
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        args = [ptr(a), ctypes.c_uint64(a.shape[0]), ptr(b), ctypes.c_uint64(b.shape[0]), ptr(c)]
+        if rrms is not None:
+            args.append(ptr(rrms))
+        if residual is not None:
+            args.append(ptr(residual))
+        grid = (max(1, a.shape[0] // m["M_PER_BLOCK"]), max(1, b.shape[0] // m["N_PER_BLOCK"]), 1)
+        self.kernel.launch(stream, grid, (m["THREADS_PER_BLOCK"], 1, 1), m["SMEM_BYTES"], *args)
+
+
+class AttnObject:
+    """The attention kernel object with AttnKernel's launch interface for one sequence (attn.rs:412-447)."""
+
+    def __init__(self, stream, config, name: str):
+        self.config = config
+        self.kernel = CubinKernel(stream, build_attn(stream, config, name))
+
+    def launch(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l=None, window_size=0):
+        c, m = self.config, self.kernel.meta
+        seq = q.shape[0]
+        if q.dim() != 2 or seq % m["Q_PER_BLOCK"] != 0:
+            raise X17Error(f"attention kernel object takes one sequence [seq, q_stride] with seq a multiple of {m['Q_PER_BLOCK']}, "
+                           f"got {list(q.shape)}")
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+        heads_per_cta = max(128 // c.head_dim, 1)
+        self.kernel.launch(stream, (seq // m["Q_PER_BLOCK"], max(1, c.n_heads // heads_per_cta), 1), (m["THREADS_PER_BLOCK"], 1, 1),
+                           m["SMEM_BYTES"], ctypes.c_uint64(seq), ptr(q), ptr(kv), ptr(sink_k), ptr(sink_v),
+                           ptr(attn_temperature), ptr(out), ptr(l), ctypes.c_uint64(window_size))
