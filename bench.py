@@ -672,6 +672,9 @@ def main():
     ap.add_argument("--sequential", action="store_true", help="block workload: RMSNorm before each sub-block (eight launches)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
                     "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W; qkvg M,Dm,H,D")
+    ap.add_argument("--attn-schedule", default="persistent", choices=["persistent", "per_tile"],
+                    help="attention kernel: the persistent one (default) or one CTA per 128-query tile")
+    ap.add_argument("--attn-item-tiles", type=int, default=0, help="persistent attention: query tiles per item (0 = per launch)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()
@@ -690,6 +693,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     stream = device.CudaStream(local)
+    from x17ai_b200 import kernels as K
+    K.set_attn_schedule(K.ATTN_PER_TILE if args.attn_schedule == "per_tile" else K.ATTN_PERSISTENT, args.attn_item_tiles)
     w = WORKLOADS[args.workload](stream, dev, args)
     if args.sequential:
         if args.workload != "block":

@@ -19,6 +19,18 @@ pytestmark = pytest.mark.gpu
 ALL = 1 << 20
 
 
+@pytest.fixture(autouse=True, params=["persistent", "persistent_runs_of_3", "persistent_runs_of_1", "per_tile"])
+def attn_schedule(request):
+    """Every test of this file runs on both attention kernels; the persistent one also with short runs of
+    query tiles per item, so that small shapes cross item boundaries and take the unfused first sweep."""
+    from x17ai_b200 import kernels as K
+    which, tiles = {"persistent": (K.ATTN_PERSISTENT, 0), "persistent_runs_of_3": (K.ATTN_PERSISTENT, 3),
+                    "persistent_runs_of_1": (K.ATTN_PERSISTENT, 1), "per_tile": (K.ATTN_PER_TILE, 0)}[request.param]
+    K.set_attn_schedule(which, tiles)
+    yield request.param
+    K.set_attn_schedule()
+
+
 def _inputs(rng, B, S, H, D, kv_pad=0, q_pad=0):
     q = formats.quantize_fixedi8(rng.standard_normal((B, S, H * D + q_pad)))
     k = rng.standard_normal((B, S, H, D))

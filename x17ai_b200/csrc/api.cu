@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "attn.cuh"
+#include "attn_stream.cuh"
 #include "decode.cuh"
 #include "diag.hpp"
 #include "gemm.cuh"
@@ -26,6 +27,8 @@ using x17::static_diag;
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_attn_schedule{X17AI_B200_ATTN_PERSISTENT};
+std::atomic<unsigned> g_attn_item_tiles{0};   // 0 = chosen per launch
 std::mutex g_capture_mutex;
 std::unordered_map<void *, CUcontext> g_capture_ctx;   // streams between graph_begin and graph_end
 
@@ -244,24 +247,61 @@ x17ai_DiagnosticBuffer *attn_launch(
 	p.dbg_p = dbg_p;
 	p.dbg_o = dbg_o;
 
-	dim3 grid(unsigned((seq_len + x17::attn_cfg::BQ - 1) / x17::attn_cfg::BQ), unsigned(cfg->n_heads),
-			  unsigned(batch));
-	dim3 block(x17::attn_cfg::THREADS);
-	auto go = [&](auto kernel, uint32_t smem) -> cudaError_t {
-		// at least 80 KB so that no more than two CTAs (2 x 256 TMEM columns) share an SM
-		smem = smem < 80u * 1024u ? 80u * 1024u : smem;
-		cudaError_t ce = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-		if (ce != cudaSuccess) return ce;
-		kernel<<<grid, block, smem, reinterpret_cast<cudaStream_t>(stream)>>>(tm_q, tm_kv, p);
-		return cudaSuccess;
-	};
 	cudaError_t ce;
-	if (d == 128) {
-		ce = go(x17::attn_fwd_kernel<128, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<128>());
-	} else if (d == 64) {
-		ce = go(x17::attn_fwd_kernel<64, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<64>());
+	if (g_attn_schedule.load(std::memory_order_relaxed) == X17AI_B200_ATTN_PERSISTENT) {
+		// items = runs of consecutive query tiles of one (batch, head), dealt round-robin to one CTA per
+		// SM. Long runs pay the unfused maximum sweep of their first tile less often; short runs
+		// balance the SMs: halve the run while fewer than two items per SM come out.
+		x17::AttnItemPlan plan{};
+		plan.n_qtiles = uint32_t((seq_len + x17::attn_stream_cfg::BQ - 1) / x17::attn_stream_cfg::BQ);
+		uint32_t const sms = uint32_t(scope.state().sm_count);
+		uint64_t const bh = uint64_t(batch) * cfg->n_heads;
+		uint32_t tiles = g_attn_item_tiles.load(std::memory_order_relaxed);
+		if (tiles == 0) {
+			tiles = 16;
+			while (tiles > 4 && bh * ((plan.n_qtiles + tiles - 1) / tiles) < 2ull * sms) tiles /= 2;
+		}
+		plan.tiles_per_item = tiles < plan.n_qtiles ? tiles : plan.n_qtiles;
+		plan.chunks = (plan.n_qtiles + plan.tiles_per_item - 1) / plan.tiles_per_item;
+		uint64_t const items = bh * plan.chunks;
+		if (items >= (uint64_t(1) << 31)) {
+			return make_diag("x17ai_b200: attention shape out of range", who, ": attention shape out of range");
+		}
+		plan.n_items = uint32_t(items);
+		dim3 grid(plan.n_items < sms ? plan.n_items : sms);
+		dim3 block(x17::attn_stream_cfg::THREADS);
+		auto go = [&](auto kernel, uint32_t smem) -> cudaError_t {
+			cudaError_t e2 = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+			if (e2 != cudaSuccess) return e2;
+			kernel<<<grid, block, smem, reinterpret_cast<cudaStream_t>(stream)>>>(tm_q, tm_kv, p, plan);
+			return cudaSuccess;
+		};
+		if (d == 128) {
+			ce = go(x17::attn_fwd_stream_kernel<128, DEBUG, FP8PV>, x17::attn_stream_cfg::smem_bytes<128>());
+		} else if (d == 64) {
+			ce = go(x17::attn_fwd_stream_kernel<64, DEBUG, FP8PV>, x17::attn_stream_cfg::smem_bytes<64>());
+		} else {
+			ce = go(x17::attn_fwd_stream_kernel<32, DEBUG, FP8PV>, x17::attn_stream_cfg::smem_bytes<32>());
+		}
 	} else {
-		ce = go(x17::attn_fwd_kernel<32, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<32>());
+		dim3 grid(unsigned((seq_len + x17::attn_cfg::BQ - 1) / x17::attn_cfg::BQ), unsigned(cfg->n_heads),
+				  unsigned(batch));
+		dim3 block(x17::attn_cfg::THREADS);
+		auto go = [&](auto kernel, uint32_t smem) -> cudaError_t {
+			// at least 80 KB so that no more than two CTAs (2 x 256 TMEM columns) share an SM
+			smem = smem < 80u * 1024u ? 80u * 1024u : smem;
+			cudaError_t e2 = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+			if (e2 != cudaSuccess) return e2;
+			kernel<<<grid, block, smem, reinterpret_cast<cudaStream_t>(stream)>>>(tm_q, tm_kv, p);
+			return cudaSuccess;
+		};
+		if (d == 128) {
+			ce = go(x17::attn_fwd_kernel<128, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<128>());
+		} else if (d == 64) {
+			ce = go(x17::attn_fwd_kernel<64, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<64>());
+		} else {
+			ce = go(x17::attn_fwd_kernel<32, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<32>());
+		}
 	}
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
@@ -683,6 +723,14 @@ x17ai_DiagnosticBuffer *x17ai_b200_graph_destroy(x17ai_b200_Graph *graph, x17ai_
 }
 
 uint64_t x17ai_b200_graph_kernel_nodes(x17ai_b200_Graph const *graph) { return graph ? graph->kernel_nodes : 0; }
+
+int x17ai_b200_set_attn_schedule(int schedule, unsigned tiles_per_item) {
+	if (schedule != X17AI_B200_ATTN_PERSISTENT && schedule != X17AI_B200_ATTN_PER_TILE) return -1;
+	if (tiles_per_item > 4096) return -1;
+	g_attn_schedule.store(schedule, std::memory_order_relaxed);
+	g_attn_item_tiles.store(tiles_per_item, std::memory_order_relaxed);
+	return 0;
+}
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_meta(x17ai_AttnConfig const *cfg, x17ai_AttnMeta *meta) {
 	char const *who = "x17ai_b200_attn_meta()";
