@@ -672,8 +672,8 @@ def main():
     ap.add_argument("--sequential", action="store_true", help="block workload: RMSNorm before each sub-block (eight launches)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
                     "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W; qkvg M,Dm,H,D")
-    ap.add_argument("--attn-schedule", default="persistent", choices=["persistent", "per_tile"],
-                    help="attention kernel: the persistent one (default) or one CTA per 128-query tile")
+    ap.add_argument("--attn-schedule", default="per_tile", choices=["persistent", "per_tile"],
+                    help="attention kernel: one CTA per 128-query tile (default) or the persistent one")
     ap.add_argument("--attn-item-tiles", type=int, default=0, help="persistent attention: query tiles per item (0 = per launch)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

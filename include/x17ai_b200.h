@@ -210,15 +210,16 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
 /*
  * Which kernel the three attention entry points above and below launch.  No counterpart in the
  * reference (its one kernel, cuda/attn_fwd_i8.cuh:368-619, runs one CTA per 64 queries and head group):
- *   X17AI_B200_ATTN_PERSISTENT (default): one CTA per SM walks runs of `tiles_per_item` consecutive
- *     128-query tiles of one (batch, head); probabilities stay in tensor memory and the maximum sweep of
- *     the next query tile runs inside the probability sweep of the current one.  tiles_per_item = 0
- *     lets every launch choose (16, halved down to 4 while fewer than two items per SM come out).
- *   X17AI_B200_ATTN_PER_TILE: one CTA per 128-query tile, two CTAs per SM (the kernel the kernel
- *     objects embed); tiles_per_item is ignored.
+ *   X17AI_B200_ATTN_PER_TILE (default, the faster one on configs[1]): one CTA per 128-query tile, two
+ *     CTAs per SM (the kernel the kernel objects embed); tiles_per_item is ignored.
+ *   X17AI_B200_ATTN_PERSISTENT: one CTA per SM walks runs of `tiles_per_item` consecutive 128-query
+ *     tiles of one (batch, head); probabilities stay in tensor memory (P.V takes its A operand from
+ *     there) and the maximum sweep of the next query tile runs inside the probability sweep of the
+ *     current one.  tiles_per_item = 0 lets every launch choose (16, halved down to 4 while fewer than
+ *     two items per SM come out).
  * Both give the same scores, probabilities and int32 accumulators; the normaliser is summed in a
- * different order, so codes may differ by one step in rare cases.  Process-wide; returns 0, or -1
- * for an unknown schedule.
+ * different order and the final rounding differs in its last step, so codes may differ by one step in
+ * rare cases.  Process-wide; returns 0, or -1 for an unknown schedule.
  */
 enum { X17AI_B200_ATTN_PERSISTENT = 0, X17AI_B200_ATTN_PER_TILE = 1 };
 int x17ai_b200_set_attn_schedule(int schedule, unsigned tiles_per_item);

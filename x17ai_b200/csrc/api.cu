@@ -27,7 +27,7 @@ using x17::static_diag;
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
-std::atomic<int> g_attn_schedule{X17AI_B200_ATTN_PERSISTENT};
+std::atomic<int> g_attn_schedule{X17AI_B200_ATTN_PER_TILE};
 std::atomic<unsigned> g_attn_item_tiles{0};   // 0 = chosen per launch
 std::mutex g_capture_mutex;
 std::unordered_map<void *, CUcontext> g_capture_ctx;   // streams between graph_begin and graph_end
@@ -513,16 +513,6 @@ size_t x17ai_b200_take_diagnostic(x17ai_DiagnosticBuffer *diag, char *dst, size_
 	x17ai_move_diagnostic(diag, x17ai_FfiBuffer{&buf, &g_fixed_vmt});
 	return buf.len;
 }
-
-#ifdef X17_ATTN_TIMELINE
-// experiment builds only: copies the recorded timeline to the host
-int x17ai_b200_experiment_times(long long *times, unsigned *counts) {
-	cudaDeviceSynchronize();
-	cudaError_t e = cudaMemcpyFromSymbol(times, x17::g_times, sizeof(long long) * 4 * 128);
-	if (e == cudaSuccess) e = cudaMemcpyFromSymbol(counts, x17::g_ntimes, sizeof(unsigned) * 4);
-	return int(e);
-}
-#endif
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg,
 													x17ai_AttnObjectDesc *desc) {

@@ -63,11 +63,7 @@ constexpr u32 O_COL = 128;
 constexpr u32 XCHG_BYTES = ROW_THREADS * 4;
 template <u32 D>
 constexpr u32 smem_bytes() {
-#ifdef X17_ATTN_TIMELINE
-	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256 + 4096;
-#else
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
-#endif
 }
 constexpr f32 MAGIC = 12582912.0f;  // 1.5 * 2^23
 constexpr u32 MAGIC_BITS = 0x4B400000u;
@@ -81,14 +77,12 @@ X17_DEV void st_shared_v4(u32 addr, u32 a, u32 b, u32 c, u32 d) {
 // N score columns of one row -> probabilities: accumulates the un-rounded exp2 into sum[4] and
 // returns rint(255 * p) packed four to a word. EDGE: only columns lo <= col < lo + span are visible.
 // The four f32 operations per element are issued as packed f32x2 instructions (two elements per
-// issue slot); the int -> float and float -> u8 conversions use the 1.5 * 2^23 trick on the FMA
-// pipe. FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
+// issue slot); int -> float is one I2FP, float -> u8 uses the 1.5 * 2^23 trick on the FMA pipe. FP8: P is written as OCP e4m3 of 256 * p instead of u8 of 255 * p.
 template <bool EDGE, bool FP8 = false, u32 N = 32>
 X17_DEV void softmax_chunk(u32 const (&r)[N], u32 col0, f32 temp, f32 neg_m, u32 lo, u32 span,
 							  f32 (&sum)[4], u32 (&pk)[N / 4]) {
 	using namespace attn_cfg;
 	u64 const s256 = pack_f32x2(256.0f, 256.0f);
-	u64 const neg_magic2 = pack_f32x2(-MAGIC, -MAGIC);
 	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
 	u64 const temp2 = pack_f32x2(temp, temp);
 	u64 const negm2 = pack_f32x2(neg_m, neg_m);
@@ -101,9 +95,9 @@ X17_DEV void softmax_chunk(u32 const (&r)[N], u32 col0, f32 temp, f32 neg_m, u32
 #pragma unroll
 		for (u32 h = 0; h < 2; ++h) {
 			u32 const i = 4 * g + 2 * h;
-			// exact int -> float without the conversion unit (|acc| < 2^22)
-			u64 const f2 = add_f32x2(pack_f32x2(__uint_as_float(r[i] + MAGIC_BITS), __uint_as_float(r[i + 1] + MAGIC_BITS)),
-									 neg_magic2);
+			// exact int -> float (|acc| < 2^24) with the ALU's I2FP: one instruction, where adding 1.5 * 2^23 to
+			// the bits and subtracting it again as a float takes one and a half
+			u64 const f2 = pack_f32x2(__int2float_rn(i32(r[i])), __int2float_rn(i32(r[i + 1])));
 			u64 const x2 = fma_f32x2(f2, temp2, negm2);
 			f32 x0, x1;
 			unpack_f32x2(x2, x0, x1);
@@ -152,23 +146,6 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 	}
 }
 
-#ifdef X17_ATTN_TIMELINE
-// Diagnostic build (-DX17_ATTN_TIMELINE, never the shipped library): timeline of one CTA, recorded
-// in shared memory and copied out at the end, read back through x17ai_b200_experiment_times:
-// g_times[role][event] = clock64() << 8 | tag; roles: 0 TMA, 1 MMA, 2 row warp 2, 3 row warp 6
-__device__ long long g_times[4][128];
-__device__ unsigned g_ntimes[4];
-#define X17_T(role, tag)                                                       \
-	do {                                                                       \
-		if ((threadIdx.x & 31) == 0 && t_n < 127) {                            \
-			t_buf[(role) * 128 + t_n] = (clock64() << 8) | (tag);              \
-			++t_n;                                                             \
-		}                                                                      \
-	} while (0)
-#else
-#define X17_T(role, tag) do {} while (0)
-#endif
-
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
 // accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
 // The tensor maps are reached through pointers: kernel parameters for the library's entry points, maps
@@ -207,10 +184,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		reinterpret_cast<volatile u32 *>(smem_gen + BAR_OFF + 8 * (2 * STAGES + 8));
 	volatile u32 *const abort_flag = tmem_slot_gen + 1;
 	WaitCtx const ctx{abort_flag, p.status};
-#ifdef X17_ATTN_TIMELINE
-	long long *const t_buf = reinterpret_cast<long long *>(smem_gen + BAR_OFF + 256);
-	u32 t_n = 0;
-#endif
 
 	u32 const warp = threadIdx.x >> 5;
 	u32 const lane = threadIdx.x & 31;
@@ -268,7 +241,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				tma_load_3d(s_ring + s * TILE_BYTES, tm_kv_ptr, full_bar(s), i32(2 * head * D + item * D),
 							i32(t * BKV), i32(batch));
 				++it;
-				X17_T(0, 1);
 				return true;
 			};
 			// sweep 1: K tiles. sweep 2, in the order the MMA warp consumes them:
@@ -301,19 +273,16 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				u32 const ph = (it / STAGES) & 1;
 				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
 				tc_fence_after();
-				X17_T(1, 5);
 				u64 const bdesc = ring_desc + u64(s * (TILE_BYTES >> 4));
 #pragma unroll
 				for (u32 ks = 0; ks < D / 32; ++ks) {
 					mma_i8_ss(tmem_base + b * BKV, q_desc + 2 * ks, bdesc + 2 * ks, idesc_qk, ks != 0);
 				}
-				X17_T(1, 6);
 				tc_commit(empty_bar(s));
 				tc_commit(s_full_bar(b));
 				++it;
 				use0 += b == 0 ? 1u : 0u;
 				use1 += b == 0 ? 0u : 1u;
-				X17_T(1, 2);
 				return true;
 			};
 			// O += P.V for one tile; P of that tile is in shared memory
@@ -322,7 +291,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				u32 const ph = (it / STAGES) & 1;
 				if (!mbar_wait(full_bar(s), ph, ctx, ST_WAIT_TMA_FULL, s)) return false;
 				tc_fence_after();
-				X17_T(1, 5);
 				u64 const bdesc = ring_desc + u64(s * (TILE_BYTES >> 4));
 #pragma unroll
 				for (u32 ks = 0; ks < BKV / 32; ++ks) {
@@ -336,11 +304,9 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 								  (!first || ks != 0) ? 1u : 0u);
 					}
 				}
-				X17_T(1, 6);
 				tc_commit(empty_bar(s));
 				tc_commit(pv_done_bar);
 				++it;
-				X17_T(1, 4);
 				return true;
 			};
 			// before S_b is overwritten, its previous contents must have been read
@@ -349,7 +315,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				if (used == 0) return true;
 				if (!mbar_wait(s_done_bar(b), (used - 1) & 1, ctx, ST_WAIT_S_DONE, t)) return false;
 				tc_fence_after();
-				X17_T(1, 1);
 				return true;
 			};
 
@@ -373,7 +338,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				}
 				++n_p;
 				tc_fence_after();
-				X17_T(1, 3);
 				ok = issue_pv(t == t_begin);
 			}
 			if (ok) tc_commit(o_full_bar);
@@ -417,13 +381,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
 		bool ok = true;
 		u32 const col_base = half * 64u;
-#ifdef X17_ATTN_TIMELINE
-		u32 const trole = warp == 2 ? 2u : 3u;
-		bool const tme = warp == 2 || warp == 6;
-#define X17_TR(tag) do { if (tme) X17_T(trole, tag); } while (0)
-#else
-#define X17_TR(tag) do {} while (0)
-#endif
 
 		// visible columns of this row inside tile k0: lo <= col < lo + span (only used on edge tiles)
 		auto visible = [&](u32 k0, u32 &lo, u32 &span) {
@@ -448,7 +405,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			use0 += b == 0 ? 1u : 0u;
 			use1 += b == 0 ? 0u : 1u;
 			tc_fence_after();
-			X17_TR(1);
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
@@ -460,7 +416,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
-			X17_TR(2);
 			if (edge) {
 				if (pos_t) {
 					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
@@ -516,7 +471,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			}
 			++use0;
 			tc_fence_after();
-			X17_TR(3);
 			u32 const k0 = t * BKV;
 			bool const edge = (t == t_end) || (w != 0xFFFFFFFFu && k0 + w < q0 + BQ - 1);
 			u32 lo = 0, span = BKV;
@@ -528,7 +482,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
-			X17_TR(4);
 			u32 pk0[8], pk1[8];
 			if (edge) {
 				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
@@ -537,7 +490,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				softmax_chunk<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
 				softmax_chunk<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
-			X17_TR(5);
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
 				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
 					ok = false;
@@ -550,7 +502,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			st_shared_v4(p_row + (((ch0 + 3) ^ sw) << 4), pk1[4], pk1[5], pk1[6], pk1[7]);
 			fence_proxy_async_smem();
 			mbar_arrive(p_ready_bar);
-			X17_TR(6);
 			if constexpr (DEBUG) {
 				if (row_ok) {
 					u8 *dst = p.dbg_p + (u64(batch) * p.n_heads + head) * p.seq_len * p.seq_len
@@ -570,10 +521,8 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		named_barrier_sync(1, ROW_THREADS);
 		f32 const other = xchg[xpartner];
 		f32 const both = half == 0 ? __fadd_rn(part, other) : __fadd_rn(other, part);
-		X17_TR(7);
 		if (ok && mbar_wait_warp(o_full_bar, 0, ctx, ST_WAIT_O_FULL, 0)) {
 			tc_fence_after();
-			X17_TR(8);
 			f32 const sink_e = ex2_approx(__fsub_rn(sink_s, m));
 			constexpr f32 PS = FP8PV ? 256.0f : 255.0f;  // scale of the quantised probabilities
 			f32 const total = __fmul_rn(__fadd_rn(both, sink_e), PS);
@@ -636,17 +585,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		}
 	}
 
-#ifdef X17_ATTN_TIMELINE
-	{
-		bool const sel = blockIdx.x == 20 && blockIdx.y == 3 && blockIdx.z == 0;
-		u32 const role = warp == 0 ? 0u : warp == 1 ? 1u : warp == 2 ? 2u : warp == 6 ? 3u : 9u;
-		if (sel && role < 4 && lane == 0) {
-			// each role's counter lives in the registers of its recording lane
-			g_ntimes[role] = t_n;
-			for (u32 i = 0; i < t_n; ++i) g_times[role][i] = t_buf[role * 128 + i];
-		}
-	}
-#endif
 	tc_fence_before();
 	__syncthreads();
 	if (warp == 1) {

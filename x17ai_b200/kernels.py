@@ -73,10 +73,10 @@ def _dtype_and_device(op, name, t, dtype):
 ATTN_PERSISTENT, ATTN_PER_TILE = 0, 1
 
 
-def set_attn_schedule(schedule: int = ATTN_PERSISTENT, tiles_per_item: int = 0) -> None:
-    """Process-wide choice of the attention kernel (x17ai_b200_set_attn_schedule): the persistent
-    kernel (default; `tiles_per_item` consecutive query tiles per item, 0 = chosen per launch) or the
-    one-CTA-per-query-tile kernel that the kernel objects embed."""
+def set_attn_schedule(schedule: int = ATTN_PER_TILE, tiles_per_item: int = 0) -> None:
+    """Process-wide choice of the attention kernel (x17ai_b200_set_attn_schedule): the one-CTA-per-query-tile
+    kernel (default, the one the kernel objects embed) or the persistent kernel (`tiles_per_item`
+    consecutive query tiles per item, 0 = chosen per launch)."""
     if _lib.load().x17ai_b200_set_attn_schedule(int(schedule), int(tiles_per_item)) != 0:
         raise X17Error(f"unknown attention schedule {schedule} / tiles_per_item {tiles_per_item}")
 
