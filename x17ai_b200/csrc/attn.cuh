@@ -60,7 +60,7 @@ constexpr u32 ROW_THREADS = ROW_WARPS * 32;
 constexpr u32 THREADS = 64 + ROW_THREADS;
 constexpr u32 TMEM_COLS = 256;
 constexpr u32 O_COL = 128;
-constexpr u32 XCHG_BYTES = ROW_THREADS * 4;
+constexpr u32 XCHG_BYTES = ROW_THREADS * 4 + 128 * 4;  // the row pairs' exchange area, then the head's sink values as f32
 template <u32 D>
 constexpr u32 smem_bytes() {
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
@@ -170,6 +170,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 	constexpr u32 XCHG_OFF = BQ * D + STAGES * TILE_BYTES + BQ * BKV;
 	constexpr u32 BAR_OFF = XCHG_OFF + XCHG_BYTES;
 	f32 *const xchg = reinterpret_cast<f32 *>(smem_gen + XCHG_OFF);
+	f32 *const svf = xchg + ROW_THREADS;
 	u32 const bar_base = smem_base + BAR_OFF;
 	auto full_bar = [&](u32 s) { return bar_base + 8 * s; };
 	auto empty_bar = [&](u32 s) { return bar_base + 8 * (STAGES + s); };
@@ -378,6 +379,12 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		bool const pos_t = head_t >= 0.0f;  // uniform over the CTA; row_t > 0 always
 		f32 const sink_s = __fmul_rn(__int2float_rn(sink_dot), temp);
 
+		// the head's sink values as f32, once per CTA (read in the epilogue, two named barriers later)
+		if (threadIdx.x - 64u < D) {
+			u32 const b = reinterpret_cast<u8 const *>(p.sink_v)[head * D + (threadIdx.x - 64u)];
+			svf[threadIdx.x - 64u] = FP8PV ? hw_e4m3_to_f32(b) : f32(i32(i8(b)));
+		}
+
 		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
 		bool ok = true;
 		u32 const col_base = half * 64u;
@@ -531,41 +538,47 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			constexpr u32 HALF_D = D / 2;
 			u32 const d0 = half * HALF_D;
 			u64 const out_off = u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D + d0;
-			f32 const vs = FP8PV ? __ldg(p.v_scale + head) : 1.0f;
+			f32 const vs = FP8PV ? __fmul_rn(recip, __ldg(p.v_scale + head)) : recip;
 #pragma unroll
 			for (u32 c = 0; c < HALF_D; c += 16) {
 				u32 r[16];
 				tmem_ld_32x32b_x16(tmem_base + lane_addr + O_COL + d0 + c, r);
+				f32 sv[16];
+#pragma unroll
+				for (u32 i = 0; i < 16; i += 4) {
+					float4 const s4 = *reinterpret_cast<float4 const *>(svf + d0 + c + i);
+					sv[i] = s4.x; sv[i + 1] = s4.y; sv[i + 2] = s4.z; sv[i + 3] = s4.w;
+				}
 				tmem_wait_ld();
-				uint4 const sv = __ldg(reinterpret_cast<uint4 const *>(p.sink_v + head * D + d0 + c));
-				u32 const svw[4] = {sv.x, sv.y, sv.z, sv.w};
 				if constexpr (FP8PV) {
 					// O is f32 = sum of (256 p) * e4m3(v); sink_v is e4m3 too; out = bf16(value * v_scale)
-					f32 o[16];
+					u32 o2[8];
 #pragma unroll
-					for (u32 i = 0; i < 16; ++i) {
-						f32 const svf = hw_e4m3_to_f32(svw[i >> 2] >> (8 * (i & 3)));
-						o[i] = __fmul_rn(__fmul_rn(__fmaf_rn(w_sink, svf, __uint_as_float(r[i])), recip), vs);
+					for (u32 i = 0; i < 16; i += 2) {
+						f32 const oa = __fmul_rn(__fmaf_rn(w_sink, sv[i], __uint_as_float(r[i])), vs);
+						f32 const ob = __fmul_rn(__fmaf_rn(w_sink, sv[i + 1], __uint_as_float(r[i + 1])), vs);
+						o2[i / 2] = cvt_bf16x2(oa, ob);
 					}
 					if (row_ok) {
 						uint4 *dst = reinterpret_cast<uint4 *>(static_cast<u16 *>(p.out) + out_off + c);
-						dst[0] = make_uint4(cvt_bf16x2(o[0], o[1]), cvt_bf16x2(o[2], o[3]), cvt_bf16x2(o[4], o[5]),
-											cvt_bf16x2(o[6], o[7]));
-						dst[1] = make_uint4(cvt_bf16x2(o[8], o[9]), cvt_bf16x2(o[10], o[11]), cvt_bf16x2(o[12], o[13]),
-											cvt_bf16x2(o[14], o[15]));
+						dst[0] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+						dst[1] = make_uint4(o2[4], o2[5], o2[6], o2[7]);
 					}
 				} else {
+					// rint(clamp(o * recip)) through the 1.5 * 2^23 trick: the code is the low byte
 					u32 pk[4];
 #pragma unroll
 					for (u32 g = 0; g < 4; ++g) {
 						u32 b4[4];
 #pragma unroll
 						for (u32 e = 0; e < 4; ++e) {
-							f32 const svf = f32(i32(i8((svw[g] >> (8 * e)) & 0xFFu)));
-							f32 const o = __fmaf_rn(w_sink, svf, __int2float_rn(i32(r[4 * g + e])));
-							b4[e] = u32(f32_to_fixedi8(__fmul_rn(o, recip)));
+							f32 const o = __fmaf_rn(w_sink, sv[4 * g + e], __int2float_rn(i32(r[4 * g + e])));
+							f32 const q = __fmaf_rn(o, recip, MAGIC);
+							b4[e] = __float_as_uint(fminf(fmaxf(q, MAGIC - 127.0f), MAGIC + 127.0f));
 						}
-						pk[g] = pack4(b4[0], b4[1], b4[2], b4[3]);
+						u32 const lo2 = __byte_perm(b4[0], b4[1], 0x0040);
+						u32 const hi2 = __byte_perm(b4[2], b4[3], 0x0040);
+						pk[g] = __byte_perm(lo2, hi2, 0x5410);
 					}
 					if (row_ok) {
 						*reinterpret_cast<uint4 *>(static_cast<i8 *>(p.out) + out_off + c) =
