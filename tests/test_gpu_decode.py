@@ -71,3 +71,35 @@ def test_decode_per_sequence_lengths(stream):
         ref, _ = o_attn.attn_decode_i8(q[b:b + 1], kv[b:b + 1], int(lens[b]), sk, sv, temp, 0, H, D, kv_tile=1 << 20)
         hist = code_hist(got[b], ref[0])
         assert hist[2:].sum() == 0 and hist[1] / ref.size <= 0.08
+
+
+def test_decode_per_sequence_lengths_split(stream):
+    """Per-sequence lengths through the split-KV path (partials in scratch memory, merge kernel); a length
+    above the cache's capacity is clamped to it on the device instead of reading past the cache."""
+    from x17ai_b200 import X17Error, kernels as K
+    rng = np.random.default_rng(7)
+    B, H, D, T = 4, 2, 128, 1024
+    q, kv, sk, sv, temp = _case(rng, B, H, D, T)
+    lens = np.array([1024, 333, 5000, 640], dtype=np.uint32)    # 5000 > T: treated as T
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    t = lambda a: torch.from_numpy(a).cuda()
+    tq, tkv, tsk, tsv, tt = t(q), t(kv), t(sk), t(sv), t(temp)
+    tl = torch.from_numpy(lens.view(np.int32)).cuda()
+    torch.cuda.synchronize()
+    for splits, no_alloc in ((3, False), (4, True)):
+        out = torch.zeros((B, H * D), dtype=torch.int8, device="cuda")
+        torch.cuda.synchronize()
+        kern.decode(stream, tq, tkv, T, tsk, tsv, tt, out, None, window_size=256, kv_lens=tl, n_splits=splits,
+                    no_alloc=no_alloc)
+        stream.synchronize()
+        got = out.cpu().numpy()
+        for b in range(B):
+            ref, _ = o_attn.attn_decode_i8(q[b:b + 1], kv[b:b + 1], min(int(lens[b]), T), sk, sv, temp, 256, H, D,
+                                           kv_tile=1 << 20)
+            hist = code_hist(got[b], ref[0])
+            assert hist[2:].sum() == 0 and hist[1] / ref.size <= 0.08, (splits, b, hist)
+    out = torch.zeros((B, H * D), dtype=torch.int8, device="cuda")
+    with pytest.raises(X17Error, match="kv_lens must be int32"):
+        kern.decode(stream, tq, tkv, T, tsk, tsv, tt, out, None, kv_lens=tl.to(torch.int64))
+    with pytest.raises(X17Error, match="kv_lens must be int32"):
+        kern.decode(stream, tq, tkv, T, tsk, tsv, tt, out, None, kv_lens=tl[:2])

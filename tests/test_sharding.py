@@ -64,6 +64,15 @@ def _worker(rank, world, port, q):
                                   sk[hs], sv[hs], temp[hs], W, nh, D)
         got = sharding.gather_attn(torch.from_numpy(o)[None], B, H, D, world)
         ok2 = np.array_equal(got[0].numpy(), ref)
+        # ---- attention: three sequences over two ranks (shards of two and of one sequence) ----
+        B3 = 3
+        q3 = formats.quantize_fixedi8(rng.standard_normal((B3, S, H * D)))
+        kv3 = formats.quantize_fixedi8(rng.standard_normal((B3, S, 2 * H * D)))
+        ref3 = np.stack([o_attn.attn_fwd_i8(q3[b], kv3[b], sk, sv, temp, W, H, D)[0] for b in range(B3)])
+        sh3 = sharding.attn_shard(B3, H, world, rank)
+        loc3 = np.stack([o_attn.attn_fwd_i8(q3[b], kv3[b], sk, sv, temp, W, H, D)[0] for b in range(sh3.seq_begin, sh3.seq_end)])
+        got3 = sharding.gather_attn(torch.from_numpy(loc3), B3, H, D, world)
+        ok2 = ok2 and np.array_equal(got3.numpy(), ref3)
         q.put((rank, ok1, ok2))
     finally:
         dist.destroy_process_group()

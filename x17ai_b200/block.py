@@ -185,6 +185,10 @@ class BlockForward:
     def _buffers(self, rows: int, device):
         if rows == self._rows:
             return
+        if self._graph is not None:
+            # the recording holds the addresses of the buffers that are about to be replaced
+            self._graph.destroy()
+            self._graph = None
         c, hd = self.config, self.config.attn_width
         e = lambda *shape, dtype: torch.empty(shape, dtype=dtype, device=device)
         self.q = e(rows, hd, dtype=torch.int8)

@@ -467,10 +467,10 @@ constexpr size_t NOALLOC_SCRATCH_FLOATS = size_t(1) << 20;
 static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
 
 struct NoAllocDevice {
-	std::once_flag once;
+	std::mutex mutex;
+	bool ready = false;        // set once the set-up has succeeded; a failed set-up is tried again by the next call
 	float *scratch = nullptr;  // device address of g_noalloc_scratch on this device
 	int sm_count = 0;
-	cudaError_t err = cudaSuccess;
 };
 NoAllocDevice g_noalloc_dev[MAX_DEVICES];
 
@@ -808,6 +808,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8(
 	p.kv_batch_stride = cfg->kv_stride * kv_capacity;
 	p.kv_lens = kv_lens;
 	p.kv_len = uint32_t(kv_len);
+	p.kv_capacity = uint32_t(kv_capacity);
 	p.window = window_size == 0 ? 0xFFFFFFFFu : uint32_t(((window_size - 1) / 16 + 1) * 16);
 	p.sink_k = sink_k;
 	p.sink_v = sink_v;
@@ -895,13 +896,29 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8_noalloc(
 	NoAllocDevice &nd = g_noalloc_dev[int(dev)];
 	// First call on this device (with the device current): resolve the device address of the
 	// scratch array. In host code the array's name is only a stand-in, not a device pointer.
-	std::call_once(nd.once, [&] {
-		nd.err = cudaGetSymbolAddress(reinterpret_cast<void **>(&nd.scratch), g_noalloc_scratch);
-		if (nd.err == cudaSuccess) nd.err = cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, int(dev));
-	});
-	if (nd.err != cudaSuccess || nd.scratch == nullptr) {
-		return make_diag("x17ai_b200: scratch set-up failed", who, ": cudaGetSymbolAddress failed: ",
-						 cudaGetErrorString(nd.err));
+	// Only a successful set-up is remembered: after a failure (a first call made inside a stream capture, a
+	// transient error) the next call tries again.
+	{
+		std::lock_guard<std::mutex> lock(nd.mutex);
+		if (!nd.ready) {
+			int major = 0;
+			cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, int(dev));
+			if (e == cudaSuccess && major != 10) {
+				return make_diag("x17ai_b200: device not supported", who, ": this library needs an sm_100 GPU");
+			}
+			float *ptr = nullptr;
+			if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch);
+			int sms = 0;
+			if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, int(dev));
+			if (e != cudaSuccess || ptr == nullptr) {
+				(void)cudaGetLastError();
+				return make_diag("x17ai_b200: scratch set-up failed", who, ": cudaGetSymbolAddress failed: ",
+								 cudaGetErrorString(e));
+			}
+			nd.scratch = ptr;
+			nd.sm_count = sms;
+			nd.ready = true;
+		}
 	}
 	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 	size_t const pairs = batch * cfg->n_heads;
@@ -926,6 +943,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_decode_i8_noalloc(
 	p.kv_batch_stride = cfg->kv_stride * kv_capacity;
 	p.kv_lens = kv_lens;
 	p.kv_len = uint32_t(kv_len);
+	p.kv_capacity = uint32_t(kv_capacity);
 	p.window = window_size == 0 ? 0xFFFFFFFFu : uint32_t(((window_size - 1) / 16 + 1) * 16);
 	p.sink_k = sink_k;
 	p.sink_v = sink_v;

@@ -24,8 +24,9 @@ struct DecodeParams {
 	u64 q_stride;
 	i8 const *kv;         // [B, T, H*2*D], per head [K(D) | V(D)]
 	u64 kv_stride, kv_batch_stride;
-	u32 const *kv_lens;   // [B] or null (then kv_len)
+	u32 const *kv_lens;   // [B] or null (then kv_len); entries above kv_capacity are clamped to it
 	u32 kv_len;
+	u32 kv_capacity;      // rows of one sequence's cache
 	u32 window;           // rounded up to 16; 0xFFFFFFFF = unbounded
 	i8 const *sink_k, *sink_v;
 	f32 const *temperature;
@@ -89,7 +90,7 @@ attn_decode_kernel(const DecodeParams p) {
 	u32 const grp = lane / LPR;        // which row of the instruction this lane works on
 	u32 const sub = lane % LPR;        // which 16-byte chunk of the row
 
-	u32 const kv_len = p.kv_lens ? p.kv_lens[batch] : p.kv_len;
+	u32 const kv_len = p.kv_lens ? min(p.kv_lens[batch], p.kv_capacity) : p.kv_len;
 	u32 const w = p.window;
 	u32 const k_lo = (w == 0xFFFFFFFFu || kv_len < w) ? 0u : kv_len - w;
 	u32 const n_keys = kv_len - k_lo;
@@ -117,6 +118,7 @@ attn_decode_kernel(const DecodeParams p) {
 	}
 
 	u32 const step = WARPS * RPI * UNROLL;
+	u32 since_flush = 0;  // an int32 accumulator takes at most 4 * 255 * 127 per step: flush long before 2^31
 	for (u32 t0 = s_lo + (warp * UNROLL) * RPI; t0 < s_hi; t0 += step) {
 		// ---- scores of UNROLL rows per group ----
 		uint4 kq[UNROLL];
@@ -144,7 +146,9 @@ attn_decode_kernel(const DecodeParams p) {
 			smax = fmaxf(smax, s[u]);
 		}
 		// ---- online softmax with lazy flush of the int32 accumulators ----
-		if (smax > m) {
+		if (smax > m || ++since_flush >= 8192u) {
+			since_flush = 0;
+			smax = fmaxf(smax, m);
 			f32 const a = ex2_approx(m - smax);
 #pragma unroll
 			for (u32 i = 0; i < 16; ++i) {
@@ -250,7 +254,7 @@ attn_decode_merge_kernel(const DecodeParams p) {
 	u32 const head = blockIdx.x;
 	u32 const batch = blockIdx.y;
 	u32 const d = threadIdx.x;
-	u32 const kv_len = p.kv_lens ? p.kv_lens[batch] : p.kv_len;
+	u32 const kv_len = p.kv_lens ? min(p.kv_lens[batch], p.kv_capacity) : p.kv_len;
 	u32 const w = p.window;
 	u32 const n_att = (kv_len < w ? kv_len : w) + 4u;
 	f32 const base_t = f32((1.0 / 64.0) * (D == 128 ? 0.08838834764831845 : D == 64 ? 0.125 : 0.17677669529663687));

@@ -154,7 +154,11 @@ class GemmObject:
         self.kernel = CubinKernel(stream, build_gemm(stream, config, name))
 
     def launch(self, stream, a, b, c, rrms=None, residual=None):
+        from . import kernels as K
         m = self.kernel.meta
+        # the same checks as GemmKernel.launch (tensor_check.rs:19-101, gemm.rs:591-641): a wrongly sized
+        # output would be written out of bounds
+        K.GemmKernel(self.config).check_shapes(a, b, c, rrms, residual)
         ptr = lambda t: ctypes.c_void_p(t.data_ptr())
         args = [ptr(a), ctypes.c_uint64(a.shape[0]), ptr(b), ctypes.c_uint64(b.shape[0]), ptr(c)]
         if rrms is not None:
@@ -173,13 +177,19 @@ class AttnObject:
         self.kernel = CubinKernel(stream, build_attn(stream, config, name))
 
     def launch(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l=None, window_size=0):
+        from . import kernels as K
         c, m = self.config, self.kernel.meta
-        seq = q.shape[0]
-        if q.dim() != 2 or seq % m["Q_PER_BLOCK"] != 0:
+        if q.dim() != 2 or q.shape[0] % m["Q_PER_BLOCK"] != 0:
             raise X17Error(f"attention kernel object takes one sequence [seq, q_stride] with seq a multiple of {m['Q_PER_BLOCK']}, "
                            f"got {list(q.shape)}")
-        ptr = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else 0)
         heads_per_cta = max(128 // c.head_dim, 1)
-        self.kernel.launch(stream, (seq // m["Q_PER_BLOCK"], max(1, c.n_heads // heads_per_cta), 1), (m["THREADS_PER_BLOCK"], 1, 1),
+        if c.n_heads % heads_per_cta != 0:   # attn.rs:108-113: the grid has one CTA per group of 128 / head_dim heads
+            raise X17Error(f"attention kernel config requires n_heads to be a multiple of {heads_per_cta} at head_dim "
+                           f"{c.head_dim}, got {c.n_heads}")
+        if window_size % 16 != 0:
+            raise X17Error(f"attention window_size must be zero or divisible by 16, got {window_size}")
+        batch, seq = K.AttnKernel(c)._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+        self.kernel.launch(stream, (seq // m["Q_PER_BLOCK"], c.n_heads // heads_per_cta, 1), (m["THREADS_PER_BLOCK"], 1, 1),
                            m["SMEM_BYTES"], ctypes.c_uint64(seq), ptr(q), ptr(kv), ptr(sink_k), ptr(sink_v),
                            ptr(attn_temperature), ptr(out), ptr(l), ctypes.c_uint64(window_size))

@@ -211,6 +211,12 @@ class AttnKernel:
         matrix_shape("decode", "out", out, (batch, c.o_stride), DTYPE_INT8)
         if l is not None:
             matrix_shape("decode", "l", l, (batch, c.n_heads), DTYPE_F32)
+        if kv_lens is not None:
+            # read on the device as u32 [batch]; lengths above the cache's capacity are clamped there
+            if kv_lens.dtype not in (torch.int32, torch.uint32) or tuple(kv_lens.shape) != (batch,):
+                raise X17Error(f"decode input kv_lens must be int32 [{batch}], got {kv_lens.dtype} {list(kv_lens.shape)}")
+            if not kv_lens.is_cuda or not kv_lens.is_contiguous():
+                raise X17Error("decode input kv_lens must be a contiguous tensor on device cuda")
         cfg = c._c()
         entry = self._lib.x17ai_b200_attn_decode_i8_noalloc if no_alloc else self._lib.x17ai_b200_attn_decode_i8
         check(entry(
@@ -258,6 +264,14 @@ class GemmKernel:
 
     def launch(self, stream, a, b, c, rrms=None, residual=None):
         g = self.config
+        a_rows = self.check_shapes(a, b, c, rrms, residual)
+        cfg = g._c()
+        check(self._lib.x17ai_b200_gemm_fwd(stream.handle, ctypes.byref(cfg), _ptr(a), a_rows, _ptr(b), g.b_rows,
+                                            _ptr(c), _ptr(rrms), _ptr(residual)))
+
+    def check_shapes(self, a, b, c, rrms=None, residual=None) -> int:
+        """BasicGemmLauncher's argument checks (gemm.rs:591-641, tensor_check.rs:19-101); returns the row count."""
+        g = self.config
         a_rows, _ = matrix_shape("gemm", "a", a, (None, g.a_cols), g.a_dtype)
         split = g.a_dtype == DTYPE_E4M3 and g.b_dtype == DTYPE_INT8
         if split:  # b is the [b_rows, 2 * a_cols] e4m3 buffer made by split_i8_weights
@@ -274,9 +288,7 @@ class GemmKernel:
             if residual is None:
                 raise X17Error("gemm residual epilogue needs the residual input")
             matrix_shape("gemm", "residual", residual, (a_rows, g.b_rows // 2), DTYPE_INT8)
-        cfg = g._c()
-        check(self._lib.x17ai_b200_gemm_fwd(stream.handle, ctypes.byref(cfg), _ptr(a), a_rows, _ptr(b), g.b_rows,
-                                            _ptr(c), _ptr(rrms), _ptr(residual)))
+        return a_rows
 
 
 def _proj_scale(inputs: int) -> float:

@@ -69,14 +69,25 @@ def gather_rows(local, rows_total: int, world: int, tile: int = 128, group=None)
 
 
 def gather_attn(local, batch: int, n_heads: int, head_dim: int, world: int, group=None):
-    """all_gather of attention outputs [seqs, S, heads*D] made by `attn_shard` into [batch, S, H*D]."""
+    """all_gather of attention outputs [seqs, S, heads*D] made by `attn_shard` into [batch, S, H*D].
+    Shards of different sizes (a batch or a head count that the ranks do not divide) are padded to the
+    largest one for the collective, as `gather_rows` does, so every rank sends the same count."""
     import torch
     import torch.distributed as dist
     shards = [attn_shard(batch, n_heads, world, r) for r in range(world)]
-    parts = [torch.empty_like(local) for _ in range(world)]   # equal-sized shards (world divides the units)
-    dist.all_gather(parts, local.contiguous(), group=group)
     s_len = local.shape[1]
+    seqs = max(sh.seq_end - sh.seq_begin for sh in shards)
+    cols = max(sh.head_end - sh.head_begin for sh in shards) * head_dim
+    if local.shape[0] > seqs or local.shape[2] > cols:
+        raise ValueError(f"local shard {tuple(local.shape)} is larger than any shard of this partition")
+    buf = local.contiguous()
+    if tuple(local.shape) != (seqs, s_len, cols):
+        buf = torch.zeros((seqs, s_len, cols), dtype=local.dtype, device=local.device)
+        buf[: local.shape[0], :, : local.shape[2]] = local
+    parts = [torch.empty_like(buf) for _ in range(world)]
+    dist.all_gather(parts, buf, group=group)
     out = torch.empty((batch, s_len, n_heads * head_dim), dtype=local.dtype, device=local.device)
     for p, sh in zip(parts, shards):
-        out[sh.seq_begin:sh.seq_end, :, sh.head_begin * head_dim:sh.head_end * head_dim] = p
+        nb, nc = sh.seq_end - sh.seq_begin, (sh.head_end - sh.head_begin) * head_dim
+        out[sh.seq_begin:sh.seq_end, :, sh.head_begin * head_dim:sh.head_end * head_dim] = p[:nb, :, :nc]
     return out
