@@ -3,20 +3,19 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload (N = 1): the prefill-scale int8 sliding-window attention forward
-(batch 8, 32 heads, seq 8192, head_dim 128, window 1024), one launch over the whole batch per
-step, synthetic seeded inputs.  With N > 1 (torchrun, one rank per GPU) every rank runs the same
-per-GPU workload on its own shard of an N-times larger batch: (batch, head) units are
-independent, so there is no data-path collective (weak scaling).
+Headline workload: the prefill-scale int8 sliding-window attention forward (configs[1]: batch 8, 32 heads,
+seq 8192, head_dim 128, window 1024), synthetic seeded inputs. With N > 1 (torchrun, one rank per GPU) the
+FIXED problem is sharded: rank r takes its (sequence, head) units of the one batch (x17ai_b200.sharding.attn_shard),
+no data moves inside the path, "scaling": "strong". Beside the compute-only number the line carries the same
+step with an NCCL all-gather of the outputs inside it, and with that gather chunked and overlapped.
 
-One JSON line on stdout (rank 0).  `value` is measured with inputs resident in HBM; `e2e` goes
-through the C ABI with host buffers (pinned), host->device and device->host copies inside the
-timed region.  `roofline.achieved` uses the average kernel duration from CUDA events recorded on
-the launching stream.  `--impl reference` times the CPU restatement of the reference's algorithm
-(oracle/) on the host cores on a bounded sample of the same workload.
-
-Other workloads (`--workload ffn_i8 | ffn_f8 | decode | rms_norm | qkv`) print the same kind of
-line for the other kernels of the path.
+One JSON line on stdout (rank 0). `value` is measured with inputs resident in HBM; `e2e` goes through the C ABI
+with host buffers (pinned), host->device and device->host copies inside the timed region. `roofline.achieved`
+uses the average kernel duration from CUDA events recorded on the launching stream. At N = 1 the line also
+carries `workloads`: the other kernels of the path (FFN int8 / e4m3, fused projection, decode, RMSNorm, fp8 P.V,
+the block), each timed for at least half a second with its own clock record, and `ref_kernel_baseline`: the
+reference's own attention kernel compiled for sm_100a on one sequence of the same shape. `--impl reference`
+times the reference's CPU path on the host cores on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -43,6 +42,46 @@ def measured_peaks():
         return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def attn_ops(batch, n_heads, head_dim, seq_len, window):
+    """Algorithmic operation count of one attention pass: 4 * B*H*D * sum_i (min(i, W') + 1), W' = window rounded
+    up to 16 (0 = unbounded): Q.K^T and P.V of every attended key, the sink included, masked positions excluded."""
+    w = None if window == 0 else ((window - 1) // 16 + 1) * 16
+    i = np.arange(seq_len, dtype=np.int64)
+    n = i if w is None else np.minimum(i, w)
+    return 4.0 * batch * n_heads * head_dim * float((n + 1).sum())
+
+
+def library_tensor_peaks(torch, dev):
+    """cuBLAS int8 (torch._int_mm) and fp8 (torch._scaled_mm) dense rates at 8192^3 on this GPU, best of 10,
+    measured outside every timed region: a measured denominator beside the assumed 2 x bf16."""
+    out = {}
+    n = 8192
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    def best(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(10):
+            e0, e1 = ev(), ev()
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        return 2.0 * n ** 3 / min(ts) / 1e12
+    try:
+        a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev)
+        b = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev).t()
+        out["int8_tops"] = best(lambda: torch._int_mm(a, b))
+    except Exception as e:   # a torch build without the op: report why, keep going
+        out["int8_error"] = str(e)[:80]
+    try:
+        a8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        out["fp8_tflops"] = best(lambda: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+    except Exception as e:
+        out["fp8_error"] = str(e)[:80]
+    return out
 
 
 class ClockSampler:
@@ -125,44 +164,99 @@ def dist_env():
 # workloads: each returns an object with .step(), .e2e_step(), .ops, .bytes, .units ...
 
 class AttnPrefill:
-    """configs[1]: B8 H32 S8192 D128 W1024, one batched launch per step."""
+    """configs[1]: B8 H32 S8192 D128 W1024. One batched launch per step over this rank's shard of the batch
+    (`shard` = x17ai_b200.sharding.AttnShard: whole sequences first, then head blocks of a sequence)."""
     name = "int8_sliding_window_attention_prefill"
     bound = "tensor"
     dtype = "s8"
 
-    def __init__(self, stream, device, B=8, H=32, S=8192, D=128, W=1024, seed=0):
+    def __init__(self, stream, device, B=8, H=32, S=8192, D=128, W=1024, seed=0, shard=None):
         import torch
-        from oracle import attn as o_attn
-        from x17ai_b200 import kernels as K
-        self.torch, self.stream = torch, stream
+        from x17ai_b200 import kernels as K, sharding
+        self.torch, self.stream, self.K = torch, stream, K
         self.B, self.H, self.S, self.D, self.W = B, H, S, D, W
-        g = torch.Generator(device=device).manual_seed(seed)
-        # N(0,1) values -> FixedI8 codes (x8, clamp +-127); K rows unit-RMS by construction of N(0,1)
-        def codes(*shape, std=1.0):
+        self.shard = shard or sharding.AttnShard(0, B, 0, H)
+        sh = self.shard
+        nb, nh = sh.seq_end - sh.seq_begin, sh.head_end - sh.head_begin
+        self.nb, self.nh = nb, nh
+        # N(0,1) values -> FixedI8 codes (x8, clamp +-127); every sequence has its own generator, so a rank
+        # that holds sequence b of the batch holds the same bytes whatever the number of ranks
+        def codes(g, *shape, std=1.0):
             return torch.clamp(torch.round(torch.randn(*shape, generator=g, device=device) * (8.0 * std)), -127, 127).to(torch.int8)
-        self.q = codes(B, S, H * D)
-        self.kv = codes(B, S, H * 2 * D)
-        self.kv.view(B, S, H, 2, D)[:, :, :, 1, :] = codes(B, S, H, D, std=1.3)
-        self.sink_k = codes(H, D)
-        self.sink_v = codes(H, D, std=1.3)
+        self.q = torch.empty(nb, S, H * D, dtype=torch.int8, device=device)
+        self.kv = torch.empty(nb, S, H * 2 * D, dtype=torch.int8, device=device)
+        for i, b in enumerate(range(sh.seq_begin, sh.seq_end)):
+            g = torch.Generator(device=device).manual_seed(seed * 1000 + 1 + b)
+            self.q[i] = codes(g, S, H * D)
+            self.kv[i] = codes(g, S, H * 2 * D)
+            self.kv[i].view(S, H, 2, D)[:, :, 1, :] = codes(g, S, H, D, std=1.3)
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.sink_k = codes(g, H, D)
+        self.sink_v = codes(g, H, D, std=1.3)
         self.temp = (0.5 + torch.rand(H, generator=g, device=device)).float()
-        self.out = torch.empty(B, S, H * D, dtype=torch.int8, device=device)
-        self.l = torch.empty(B, H, S, dtype=torch.float32, device=device)
-        self.kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
-        self.ops = o_attn.attn_ops(B, H, D, S, W)
-        self.ref_ops = self.kern.config.n_ops(S, W) * B
-        self.tokens = B * S
-        self.units = B * H  # (sequence, head) units of this S, D, W
-        self.alg_bytes = self.q.numel() + self.kv.numel() + self.out.numel() + self.l.numel() * 4
+        self.out = torch.empty(nb, S, nh * D, dtype=torch.int8, device=device)     # this shard's heads only
+        self.l = torch.empty(nb, nh, S, dtype=torch.float32, device=device)
+        self.kern = K.AttnKernel(K.AttnKernelConfig(nh, D, H * D, 2 * H * D, nh * D))
+        self.ops_total = attn_ops(B, H, D, S, W)             # the whole (fixed) problem
+        self.ops = attn_ops(nb, nh, D, S, W)                 # this rank's part
+        self.ref_ops = K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D).n_ops(S, W) * B
+        self.tokens_total = B * S
+        self.tokens = nb * S
+        self.units = nb * nh  # (sequence, head) units of this S, D, W
+        self.alg_bytes = nb * S * nh * D * 4 + self.l.numel() * 4   # q + k + v + out of the shard's heads, L
         self.launches_per_step = 1
         self.config = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H,
                        "seq_len": S, "head_dim": D, "window": W,
-                       "l2": "inputs (q+kv+out = %.0f MB) larger than the 126 MB L2" % (self.alg_bytes / 1e6)}
+                       "l2": "inputs (q+kv+out = %.0f MB per GPU) larger than the 126 MB L2" % (self.alg_bytes / 1e6)}
         torch.cuda.synchronize()
 
     def step(self):
-        self.kern.launch(self.stream, self.q, self.kv, self.sink_k, self.sink_v, self.temp, self.out, self.l, self.W)
+        self.kern.launch_head_block(self.stream, self.q, self.kv, self.sink_k, self.sink_v, self.temp, self.out, self.l,
+                                    self.W, self.shard.head_begin)
 
+    # ---- the gather of the outputs (a consumer that wants the whole tensor on every GPU) ----
+    def gather_setup(self, world, n_chunks=4):
+        """Buffers for the two gathered forms: the whole shard after the kernel, and chunk by chunk (sequence x
+        head block, each chunk's output contiguous) with chunk i's all-gather under chunk i + 1's kernel."""
+        t, K = self.torch, self.K
+        self.world = world
+        self.ext = t.cuda.ExternalStream(self.stream.handle)
+        self.comm = t.cuda.Stream()
+        self.gathered = t.empty((world,) + tuple(self.out.shape), dtype=t.int8, device=self.out.device)
+        hb_count = max(1, -(-n_chunks // self.nb))           # head blocks per sequence
+        while self.nh % hb_count:
+            hb_count -= 1
+        hb = self.nh // hb_count
+        self.chunks = [(i, j * hb) for i in range(self.nb) for j in range(hb_count)]
+        self.chunk_kern = K.AttnKernel(K.AttnKernelConfig(hb, self.D, self.H * self.D, 2 * self.H * self.D, hb * self.D))
+        self.chunk_out = [t.empty(self.S, hb * self.D, dtype=t.int8, device=self.out.device) for _ in self.chunks]
+        self.chunk_l = t.empty(hb, self.S, dtype=t.float32, device=self.out.device)
+        self.chunk_gathered = [t.empty((world, self.S, hb * self.D), dtype=t.int8, device=self.out.device) for _ in self.chunks]
+        self.chunk_events = [t.cuda.Event() for _ in self.chunks]
+        return {"chunks": len(self.chunks), "heads_per_chunk": hb,
+                "layout": "gathered[chunk][rank][seq][heads_per_chunk * head_dim]"}
+
+    def step_gather(self):
+        import torch.distributed as dist
+        self.step()
+        with self.torch.cuda.stream(self.ext):     # NCCL orders itself after, and the stream after NCCL
+            dist.all_gather_into_tensor(self.gathered, self.out)
+
+    def step_gather_overlapped(self):
+        import torch.distributed as dist
+        t = self.torch
+        for c, (i, h0) in enumerate(self.chunks):
+            self.chunk_kern.launch_head_block(self.stream, self.q[i], self.kv[i], self.sink_k, self.sink_v, self.temp,
+                                              self.chunk_out[c], self.chunk_l, self.W, self.shard.head_begin + h0)
+            with t.cuda.stream(self.ext):
+                self.chunk_events[c].record()
+            with t.cuda.stream(self.comm):
+                self.comm.wait_event(self.chunk_events[c])
+                dist.all_gather_into_tensor(self.chunk_gathered[c], self.chunk_out[c])
+        with t.cuda.stream(self.ext):
+            self.ext.wait_stream(self.comm)
+
+    # ---- end to end from pinned host buffers ----
     def host_buffers(self):
         t = self.torch
         self.h_q = self.q.cpu().pin_memory(); self.h_kv = self.kv.cpu().pin_memory()
@@ -176,12 +270,58 @@ class AttnPrefill:
         if not hasattr(self, "e2e_streams"):
             from x17ai_b200 import device
             self.e2e_streams = [self.stream] + [device.CudaStream(self.q.device.index) for _ in range(2)]
-        self.kern.launch_from_host(self.e2e_streams, self.h_q, self.h_kv, self.sink_k, self.sink_v, self.temp,
-                                   self.q, self.kv, self.out, self.h_out, self.l, self.W)
+        sts = self.e2e_streams
+        for i in range(self.nb):
+            st = sts[i % len(sts)]
+            st.upload(self.h_q[i].data_ptr(), self.q[i].data_ptr(), 0, self.q[i].numel())
+            st.upload(self.h_kv[i].data_ptr(), self.kv[i].data_ptr(), 0, self.kv[i].numel())
+            self.kern.launch_head_block(st, self.q[i], self.kv[i], self.sink_k, self.sink_v, self.temp, self.out[i],
+                                        self.l[i], self.W, self.shard.head_begin)
+            st.download(self.out[i].data_ptr(), self.h_out[i].data_ptr(), 0, self.out[i].numel())
 
     def e2e_sync(self):
         for st in getattr(self, "e2e_streams", [self.stream]):
             st.synchronize()
+
+    # ---- baselines ----
+    def ref_kernel_sample(self):
+        """The reference's own kernel (cuda/attn_fwd_i8.cuh compiled for sm_100a by oracle/build_ref.py, launched
+        through this library's driver shim with the reference's grid, attn.rs:438-446) on one sequence of this
+        shape: the same-GPU baseline the new kernel has to beat. None where the cubin was not built."""
+        import ctypes
+        from x17ai_b200 import device, kernel_objects
+        d = ROOT / "oracle" / "_ref" / f"attn_h{self.H}_d{self.D}"
+        if not (d / "kernel.cubin").exists() or not (d / "meta.json").exists():
+            return None
+        t = self.torch
+        k = kernel_objects.CubinKernel(self.stream, d)
+        m = k.meta
+        q, kv = self.q[0], self.kv[0]
+        out = t.empty(self.S, self.H * self.D, dtype=t.int8, device=q.device)
+        l = t.empty(self.H, self.S, dtype=t.float32, device=q.device)
+        t.cuda.synchronize()
+        ptr = lambda x: ctypes.c_void_p(x.data_ptr())
+        hpk = max(128 // self.D, 1)
+        args = (ctypes.c_uint64(self.S), ptr(q), ptr(kv), ptr(self.sink_k), ptr(self.sink_v), ptr(self.temp), ptr(out),
+                ptr(l), ctypes.c_uint64(self.W))
+        grid = (self.S // m["Q_PER_BLOCK"], self.H // hpk, 1)
+        go = lambda: k.launch(self.stream, grid, (m["THREADS_PER_BLOCK"], 1, 1), m["SMEM_BYTES"], *args)
+        for _ in range(3):
+            go()
+        timer = device.CudaTimer(self.stream)
+        n = 10
+        timer.start()
+        for _ in range(n):
+            go()
+        timer.stop()
+        self.stream.synchronize()
+        dt = timer.elapsed_seconds() / n
+        timer.destroy()
+        k.unload()
+        ops = attn_ops(1, self.H, self.D, self.S, self.W)
+        return {"value": ops / dt / 1e12, "unit": "TOPS", "ms": dt * 1e3,
+                "kernel": "the reference's attn_forward (mma.sync, 64 queries per CTA) compiled for sm_100a",
+                "sample": f"one sequence of the workload ({self.H} heads x {self.D}, {self.S} tokens, window {self.W}), {n} launches"}
 
     def cpu_sample(self, seconds_hint=15.0):
         """Oracle on a bounded sample: whole sequences of a few heads."""
@@ -193,11 +333,62 @@ class AttnPrefill:
         while True:
             o_attn.attn_head(mk(S, D), mk(S, D), mk(S, D), mk(D), mk(D), 1.0, W, kv_tile=16)
             heads += 1
-            done_ops += o_attn.attn_ops(1, 1, D, S, W)
+            done_ops += attn_ops(1, 1, D, S, W)
             if time.perf_counter() - t0 > seconds_hint:
                 break
         dt = time.perf_counter() - t0
         return done_ops / dt, f"{heads} (sequence, head) units of S={S} D={D} W={W}, oracle kv_tile=16, {dt:.1f} s"
+
+
+def reference_cpu_attention():
+    """The reference's own CPU path for this kernel: attn_one_head of its float64 PyTorch model (new_block.py:183-258),
+    timed on the case the reference can run on a CPU (batch 1, 4 heads, seq 256, head_dim 64, window 64, seed 0).
+    Needs a checkout of the reference (X17AI_REFERENCE); returns None elsewhere."""
+    ref = os.environ.get("X17AI_REFERENCE")
+    if not ref or not (Path(ref) / "new_block.py").exists():
+        return None
+    import importlib
+    import shutil
+    import tempfile
+    import torch
+    tmp = Path(tempfile.mkdtemp(prefix="x17ref_"))
+    try:
+        for f in ("new_block.py", "block_utils.py", "jsonc.py"):
+            shutil.copy(Path(ref) / f, tmp / f)
+        S, H, D, W = 256, 4, 64, 64
+        (tmp / "block.config.json").write_text(json.dumps({
+            "seq_len": S, "MODEL_DIM": H * D, "HEAD_DIM": D, "N_HEADS": H, "F_WIDTH": 256, "WINDOW_SIZE": W,
+            "L2_NORM_EPS": 2.0 ** -70, "V_SCALE_FIX": 1.3}))
+        sys.path.insert(0, str(tmp))
+        cwd = os.getcwd()
+        os.chdir(tmp)
+        try:
+            nb = importlib.import_module("new_block")
+        finally:
+            os.chdir(cwd)
+        if not hasattr(nb, "attn_one_head"):
+            return None
+        torch.manual_seed(0)
+        q = torch.randn(S, D, dtype=torch.float64); k = torch.randn(S, D, dtype=torch.float64); v = torch.randn(S, D, dtype=torch.float64)
+        sk = torch.randn(D, dtype=torch.float64); sv = torch.randn(D, dtype=torch.float64)
+        call = (q, k, v, sk, sv, torch.tensor(1.0, dtype=torch.float64))
+        nb.attn_one_head(*call)
+        best = 1e30
+        for _ in range(5):
+            t0 = time.perf_counter()
+            for _h in range(H):
+                nb.attn_one_head(*call)
+            best = min(best, time.perf_counter() - t0)
+        ops = attn_ops(1, H, D, S, W)
+        return {"value": ops / best / 1e12, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "reference",
+                "sample": f"new_block.attn_one_head (float64) on configs[0]: 1 x {H} heads x {S} tokens x {D}, window {W}, "
+                          f"best of 5, {best * 1e3:.1f} ms"}
+    except Exception:
+        return None
+    finally:
+        if str(tmp) in sys.path:
+            sys.path.remove(str(tmp))
+        shutil.rmtree(tmp, ignore_errors=True)
 
 
 class AttnPvFp8(AttnPrefill):
@@ -312,6 +503,57 @@ class Ffn:
         dt = time.perf_counter() - t0
         ops = n * (2.0 * rows * self.Dm * 2 * self.F + 2.0 * rows * self.F * 2 * self.Dm)
         return ops / dt, f"{n} x {rows} token rows of the same FFN, {dt:.1f} s"
+
+
+class FfnE4m3(Ffn):
+    """configs[3], second run: the same gated FFN with e4m3 weights and e4m3 activations, one f32 scale per tensor
+    (weights N(0, 0.02), scale = absmax / 448). Both GEMMs run as e4m3 x e4m3 on the fp8 tensor path."""
+
+    def __init__(self, stream, device, M=16384, Dm=4096, F=14336, seed=0):
+        import torch
+        from x17ai_b200 import kernels as K
+        self.torch, self.stream, self.f8 = torch, stream, True
+        self.name, self.dtype = "ffn_fwd_e4m3", "e4m3"
+        g = torch.Generator(device=device).manual_seed(seed)
+        def q8(t):   # per-tensor scale, OCP e4m3 bytes
+            scale = float(t.abs().max()) / 448.0
+            return (t / scale).to(torch.float8_e4m3fn).view(torch.uint8), scale
+        xv = torch.randn(M, Dm, generator=g, device=device)
+        self.x8, self.sx = q8(xv)
+        self.x = torch.clamp(torch.round(xv * 8.0), -127, 127).to(torch.int8)      # the residual stream (FixedI8)
+        del xv
+        self.wf, self.swf = q8(torch.randn(2 * F, Dm, generator=g, device=device) * 0.02)
+        self.wy, self.swy = q8(torch.randn(2 * Dm, F, generator=g, device=device) * 0.02)
+        self.f = torch.empty(M, F, dtype=torch.uint8, device=device)
+        self.y = torch.empty(M, Dm, dtype=torch.uint8, device=device)
+        self.k_f = K.GemmKernel(K.ffn_f_fwd_e4m3_config(Dm, F, self.sx, self.swf))
+        self.k_y = K.GemmKernel(K.ffn_y_fwd_e4m3_config(F, Dm, self.swy))
+        torch.cuda.synchronize()
+        self.M, self.Dm, self.F = M, Dm, F
+        self.ops = 2.0 * M * Dm * 2 * F + 2.0 * M * F * 2 * Dm
+        self.tokens = M
+        self.units = M
+        self.alg_bytes = M * Dm + 2 * F * Dm + M * F * 2 + 2 * Dm * F + M * Dm * 2
+        self.launches_per_step = 2
+        self.config = {"workload": "configs[3] gated FFN, e4m3 weights and activations with per-tensor scales", "tokens": M,
+                       "d_model": Dm, "hidden": F, "gemms": "e4m3 x e4m3 (kind::f8f6f4), f32 accumulation",
+                       "l2": "weights + activations (%.0f MB) larger than the 126 MB L2" % (self.alg_bytes / 1e6)}
+
+    def step(self):
+        self.k_f.launch(self.stream, self.x8, self.wf, self.f)
+        self.k_y.launch(self.stream, self.f, self.wy, self.y, residual=self.x)
+
+    def host_buffers(self):
+        t = self.torch
+        self.h_x = self.x8.cpu().pin_memory()
+        self.h_y = t.empty_like(self.y, device="cpu").pin_memory()
+        self.h2d, self.d2h = self.h_x.numel(), self.h_y.numel()
+
+    def e2e_step(self):
+        s = self.stream
+        s.upload(self.h_x.data_ptr(), self.x8.data_ptr(), 0, self.h_x.numel())
+        self.step()
+        s.download(self.y.data_ptr(), self.h_y.data_ptr(), 0, self.h_y.numel())
 
 
 class Qkvg:
@@ -574,12 +816,12 @@ class Block:
                 break
         dt = time.perf_counter() - t0
         ops = (2.0 * S * Dm * (3 * H * D) + 2.0 * S * H * D * 2 * Dm + 2.0 * S * Dm * 2 * F + 2.0 * S * F * 2 * Dm
-               + o_attn.attn_ops(1, H, D, S, W))
+               + attn_ops(1, H, D, S, W))
         return n * ops / dt, f"{n} block forwards of a {S}-token sequence at the same model shape, {dt:.1f} s"
 
 
 def _shape(args, n):
-    if not args.shape:
+    if args is None or not args.shape:
         return None
     v = [int(x) for x in args.shape.split(",")]
     if len(v) != n:
@@ -588,21 +830,32 @@ def _shape(args, n):
 
 
 WORKLOADS = {
-    "attn": lambda s, d, a=None: AttnPrefill(s, d, *(_shape(a, 5) or ())),
+    "attn": lambda s, d, a=None, **kw: AttnPrefill(s, d, *(_shape(a, 5) or ()), **kw),
     "attn_pv_fp8": lambda s, d, a=None: AttnPvFp8(s, d, *(_shape(a, 5) or ())),
     "ffn_i8": lambda s, d, a=None: Ffn(s, d, False, *(_shape(a, 3) or ())),
     "ffn_f8": lambda s, d, a=None: Ffn(s, d, True, *(_shape(a, 3) or ())),
+    "ffn_e4m3": lambda s, d, a=None: FfnE4m3(s, d, *(_shape(a, 3) or ())),
     "qkvg": lambda s, d, a=None: Qkvg(s, d, *(_shape(a, 4) or ())),
     "decode": lambda s, d, a=None: Decode(s, d, *(_shape(a, 5) or ())),
     "rms_norm": lambda s, d, a=None: RmsNorm(s, d, *(_shape(a, 2) or ())),
     "block": lambda s, d, a=None: Block(s, d, *(_shape(a, 7) or ())),
 }
+METRICS = {"attn": "int8 sliding-window attention prefill throughput",
+           "attn_pv_fp8": "attention with fp8 P.V prefill throughput", "ffn_i8": "gated FFN forward throughput",
+           "qkvg": "fused Q/KV projection throughput", "ffn_f8": "gated FFN forward throughput",
+           "ffn_e4m3": "gated FFN forward throughput (e4m3 weights and activations)",
+           "decode": "int8 decode attention KV-cache bandwidth", "rms_norm": "RMSNorm bandwidth",
+           "block": "quantized block forward throughput"}
+# the other kernels of the path, reported beside the headline at N = 1 (smaller than the headline's own case
+# only where the full one would not fit the few minutes the default run has)
+SIDE_WORKLOADS = ["ffn_i8", "ffn_f8", "ffn_e4m3", "qkvg", "attn_pv_fp8", "decode", "rms_norm", "block"]
 
 
 # ------------------------------------------------------------------------------------------------
 
 def run_reference(args, rank, world):
-    """The reference's CPU path = the CPU restatement (oracle/), all host threads, bounded sample."""
+    """The reference's CPU path, all host threads, bounded sample: its own float64 model where a checkout of the
+    reference is at hand (attention only: X17AI_REFERENCE), else the CPU restatement of its kernels (oracle/)."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
@@ -612,7 +865,7 @@ def run_reference(args, rank, world):
     except Exception:
         pass
     # build the workload description without touching a GPU
-    cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "decode": Decode,
+    cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "ffn_e4m3": Ffn, "decode": Decode,
            "rms_norm": RmsNorm, "block": Block, "qkvg": Qkvg}[args.workload]
     w = cls.__new__(cls)
     if args.workload in ("attn", "attn_pv_fp8"):
@@ -620,7 +873,7 @@ def run_reference(args, rank, world):
         w.S, w.D, w.W, B, H = 8192, 128, 1024, 8, 32
         cfg = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H, "seq_len": 8192,
                "head_dim": 128, "window": 1024}
-        unit, metric = "TOPS", "int8 sliding-window attention prefill throughput"
+        unit, metric = "TOPS", METRICS["attn"]
     elif args.workload.startswith("ffn"):
         w.Dm, w.F = 4096, 14336
         cfg = {"workload": "configs[3] gated FFN (GeGLU -> e4m3, gated residual)", "tokens": 16384, "d_model": 4096, "hidden": 14336}
@@ -651,11 +904,127 @@ def run_reference(args, rank, world):
     scale = 1e12 if unit == "TOPS" else 1e9
     v = float(np.mean(vals)) / scale
     line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "attn" else "weak",
             "vs_baseline": None, "dtype": "f32/int (numpy)", "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if args.workload == "attn":
+        ref = reference_cpu_attention()
+        if ref is not None:
+            line["cpu_reference_model"] = ref
     print(json.dumps(line), flush=True)
+
+
+def bind_to_gpu_numa_node(local):
+    """Host threads and the pinned buffers they allocate next go to the NUMA node of this rank's GPU (sysfs),
+    so that N ranks do not all stage through node 0. Returns a description for the JSON line."""
+    try:
+        bus = subprocess.run(["nvidia-smi", f"--id={local}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().splitlines()[0].strip()
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:      # NVML pads the domain to eight digits, sysfs uses four
+            bus = bus[4:]
+        node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
+        if node < 0:
+            return {"numa_node": None, "note": "the platform reports no NUMA node for the GPU"}
+        cpus = Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+        ids = set()
+        for part in cpus.split(","):
+            a, _, b = part.partition("-")
+            ids.update(range(int(a), int(b or a) + 1))
+        allowed = ids & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return {"numa_node": node, "cpus": len(allowed)}
+    except Exception as e:
+        return {"numa_node": None, "note": f"not bound: {type(e).__name__}"}
+
+
+class Runner:
+    """Times a workload: per-step CUDA-event timers on the launching stream, clocks sampled over the timed region."""
+
+    def __init__(self, torch, dist, lib, device, stream, local, world, dev):
+        self.torch, self.dist, self.lib, self.device = torch, dist, lib, device
+        self.stream, self.local, self.world, self.dev = stream, local, world, dev
+
+    def barrier(self):
+        self.stream.synchronize()
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+
+    def time_steps(self, step, steps, warmup, sync=None):
+        """(device seconds of all steps: max over ranks, mean seconds of one step, wall seconds, launches, clocks)"""
+        torch = self.torch
+        sync = sync or self.stream.synchronize
+        timers = [self.device.CudaTimer(self.stream) for _ in range(steps)]
+        for _ in range(warmup):
+            step()
+        sync()
+        sampler = ClockSampler(self.local)
+        sampler.start()
+        time.sleep(0.5)  # nvidia-smi needs a moment before its first sample
+        self.barrier()
+        launches0 = self.lib.x17ai_b200_launch_count()
+        wall0 = time.time()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            timers[i].start()
+            step()
+            timers[i].stop()
+        sync()
+        self.stream.synchronize()
+        t1 = time.perf_counter()
+        wall1 = time.time()
+        launches = self.lib.x17ai_b200_launch_count() - launches0
+        time.sleep(0.15)
+        clocks = sampler.stop(wall0, wall1)
+        dev_times = [t.elapsed_seconds() for t in timers]
+        for t in timers:
+            t.destroy()
+        status = self.stream.read_status()
+        if status != [0, 0, 0, 0]:
+            raise RuntimeError(f"device status words not clean: {status}")
+        total = torch.tensor([sum(dev_times), t1 - t0], dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(total, op=self.dist.ReduceOp.MAX)
+        return float(total[0]), float(np.mean(dev_times)), float(total[1]), int(launches), clocks
+
+    def steps_for(self, step, seconds, lo=3, hi=100000):
+        """How many steps fill `seconds` of device time (measured on three)."""
+        tm = self.device.CudaTimer(self.stream)
+        step(); self.stream.synchronize()
+        tm.start()
+        for _ in range(3):
+            step()
+        tm.stop(); self.stream.synchronize()
+        per = max(tm.elapsed_seconds() / 3, 1e-6)
+        tm.destroy()
+        return int(min(hi, max(lo, np.ceil(seconds / per))))
+
+
+def roofline(w, achieved, region_s, peaks, lib_peaks, traffic_key):
+    """`peak`: the measured denominator of MEASURED_PEAKS.json - for a tensor-bound kernel twice the cuBLAS bf16
+    rate (int8 and fp8 run at twice the bf16 rate; no int8 figure is in that file), the burst figure for a timed
+    region under a second, the sustained one for a longer region; for an HBM-bound kernel the copy bandwidth."""
+    if w.bound == "tensor":
+        burst = region_s < 1.0
+        peak = 2.0 * (peaks["bf16_burst"] if burst else peaks["bf16_sustained"])
+        r = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+             "traffic": measured_traffic(traffic_key, w.units),
+             "peak_source": f"2 x bf16 {'burst' if burst else 'sustained'} of {peaks['source']} (timed region {region_s:.2f} s)",
+             "nominal_frac": achieved / 4500.0}
+        key = "fp8_tflops" if "e4m3" in w.dtype and "s8" not in w.dtype else "int8_tops"
+        if lib_peaks.get(key):
+            r["peak_library_measured"] = lib_peaks[key]
+            r["frac_of_library_measured"] = achieved / lib_peaks[key]
+            r["peak_library_source"] = ("torch._scaled_mm e4m3" if key == "fp8_tflops" else "torch._int_mm int8") + " 8192^3, best of 10, this process"
+        return r
+    peak = peaks["hbm_gbs"]
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": measured_traffic(traffic_key, w.units), "peak_source": f"copy bandwidth of {peaks['source']}",
+            "nominal_frac": achieved / 7700.0}
 
 
 def main():
@@ -667,8 +1036,8 @@ def main():
     ap.add_argument("--workload", default="attn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--gather", action="store_true", help="N > 1: also time an NCCL all_gather of the step's output "
-                    "(reported separately as gather_ms; the path itself needs no collective)")
+    ap.add_argument("--no-side-workloads", action="store_true", help="N = 1, --workload attn: skip the `workloads` object")
+    ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the two gathered forms of the step")
     ap.add_argument("--sequential", action="store_true", help="block workload: RMSNorm before each sub-block (eight launches)")
     ap.add_argument("--shape", default="", help="override the workload shape (small cases for profiling): attn B,H,S,D,W; "
                     "ffn M,Dm,F; decode B,H,D,T,W; rms_norm M,Dm; block B,S,Dm,H,D,F,W; qkvg M,Dm,H,D")
@@ -685,60 +1054,55 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from x17ai_b200 import _lib, build, device
+    from x17ai_b200 import _lib, build, device, kernels as K, sharding
     build.build()
     lib = _lib.load()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local)      # before any pinned allocation
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     stream = device.CudaStream(local)
-    from x17ai_b200 import kernels as K
     K.set_attn_schedule(K.ATTN_PER_TILE if args.attn_schedule == "per_tile" else K.ATTN_PERSISTENT, args.attn_item_tiles)
-    w = WORKLOADS[args.workload](stream, dev, args)
+    run = Runner(torch, dist, lib, device, stream, local, world, dev)
+    strong = args.workload == "attn"
+    if strong:
+        B, H = (_shape(args, 5) or (8, 32, 0, 0, 0))[:2]
+        shard = sharding.attn_shard(B, H, world, rank)
+        w = WORKLOADS["attn"](stream, dev, args, shard=shard)
+    else:
+        w = WORKLOADS[args.workload](stream, dev, args)
     if args.sequential:
         if args.workload != "block":
             raise SystemExit("--sequential applies to --workload block")
         w.make_sequential()
         args.no_e2e = True   # the end-to-end leg times the harness form only
 
-    def barrier():
-        stream.synchronize()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+    peaks = measured_peaks()
+    lib_peaks = library_tensor_peaks(torch, dev) if rank == 0 else {}
+    torch.cuda.synchronize()
 
     # ---- device-resident timing ----
-    timers = [device.CudaTimer(stream) for _ in range(args.steps)]
-    for _ in range(args.warmup):
-        w.step()
-    sampler = ClockSampler(local)
-    sampler.start()
-    time.sleep(0.5)  # nvidia-smi needs a moment before its first sample
-    barrier()
-    launches0 = lib.x17ai_b200_launch_count()
-    wall0 = time.time()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        timers[i].start()
-        w.step()
-        timers[i].stop()
-    stream.synchronize()
-    t1 = time.perf_counter()
-    wall1 = time.time()
-    launches = lib.x17ai_b200_launch_count() - launches0
-    time.sleep(0.15)
-    clocks = sampler.stop(wall0, wall1)
-    dev_times = [t.elapsed_seconds() for t in timers]
-    status = stream.read_status()
-    if status != [0, 0, 0, 0]:
-        raise RuntimeError(f"device status words not clean: {status}")
-    # the timed region on the device: first start to last stop = sum of back-to-back steps
-    total = torch.tensor([sum(dev_times), t1 - t0], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(total, op=dist.ReduceOp.MAX)
-    dev_total, wall_total = float(total[0]), float(total[1])
-    kernel_avg = float(np.mean(dev_times))
+    dev_total, kernel_avg, wall_total, launches, clocks = run.time_steps(w.step, args.steps, args.warmup)
+    unit, scale = ("TOPS", 1e12) if w.bound == "tensor" else ("GB/s", 1e9)
+    work_rank = w.ops if w.bound == "tensor" else w.alg_bytes
+    work_job = (w.ops_total if strong else world * w.ops) if w.bound == "tensor" else world * w.alg_bytes
+    tokens_job = w.tokens_total if strong else world * w.tokens
+    value = work_job * args.steps / dev_total / scale
+    achieved = work_rank / kernel_avg / scale
+
+    # ---- the same step with the outputs gathered on every GPU ----
+    gather = None
+    if strong and world > 1 and not args.no_gather:
+        info = w.gather_setup(world)
+        n = max(5, min(args.steps, 50))
+        g_total, _, _, _, _ = run.time_steps(w.step_gather, n, 3)
+        o_total, _, _, _, _ = run.time_steps(w.step_gather_overlapped, n, 3)
+        gather = dict(info, steps=n, gathered_bytes=int(world * w.out.numel()),
+                      ms_per_step_gather_in_step=g_total / n * 1e3, value_gather_in_step=work_job * n / g_total / scale,
+                      ms_per_step_gather_overlapped=o_total / n * 1e3, value_gather_overlapped=work_job * n / o_total / scale,
+                      note="all_gather_into_tensor (NCCL) of the int8 outputs: once after the kernel; and per chunk on a "
+                           "second stream under the next chunk's kernel")
 
     # ---- end to end through the C ABI with host buffers ----
     e2e = None
@@ -748,7 +1112,7 @@ def main():
         for _ in range(2):
             w.e2e_step()
         e2e_sync()
-        barrier()
+        run.barrier()
         n_e2e = max(3, min(args.steps, 10))
         # host clock between two full synchronisations: an end-to-end step may use several
         # streams (copies of one sequence under the kernel of another), which no single
@@ -762,78 +1126,77 @@ def main():
         if world > 1:
             dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
         e2e_time = float(e2e_t[0]) / n_e2e
-        e2e = {"h2d_bytes_per_step": int(w.h2d), "d2h_bytes_per_step": int(w.d2h), "ms_per_step": e2e_time * 1e3,
-               "steps": n_e2e, "clock": "host, between stream synchronisations",
-               "streams": len(getattr(w, "e2e_streams", [stream]))}
+        e2e = {"value": work_job / e2e_time / scale, "unit": unit,
+               "h2d_bytes_per_step": int(w.h2d) * world, "d2h_bytes_per_step": int(w.d2h) * world,
+               "h2d_bytes_per_rank": int(w.h2d), "h2d_gbs_per_rank": w.h2d / e2e_time / 1e9,
+               "ms_per_step": e2e_time * 1e3, "steps": n_e2e, "clock": "host, between stream synchronisations",
+               "streams": len(getattr(w, "e2e_streams", [stream])), "host_numa": numa}
 
-    gather_ms = None
-    if args.gather and world > 1:
-        out_t = getattr(w, "out", None) if hasattr(w, "out") else getattr(w, "y", None)
-        parts = [torch.empty_like(out_t) for _ in range(world)]
-        for _ in range(2):
-            dist.all_gather(parts, out_t)
-        torch.cuda.synchronize()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for _ in range(5):
-            dist.all_gather(parts, out_t)
-        ev1.record()
-        torch.cuda.synchronize()
-        g = torch.tensor([ev0.elapsed_time(ev1) / 5], dtype=torch.float64, device=dev)
-        dist.all_reduce(g, op=dist.ReduceOp.MAX)
-        gather_ms = float(g[0])
-
-    peaks = measured_peaks()
-    if w.bound == "tensor":
-        unit, scale = "TOPS", 1e12
-        work = w.ops
-        # int8 / fp8 dense tensor rate is twice the bf16 rate; the measured denominator is the
-        # cuBLAS bf16 figure (sustained: the kernel is timed back to back inside a long step)
-        peak = 2.0 * peaks["bf16_sustained"]
-        peak_note = f"2 x bf16 sustained of {peaks['source']}"
-        r_unit = "TFLOP/s"
-    else:
-        unit, scale = "GB/s", 1e9
-        work = w.alg_bytes
-        peak = peaks["hbm_gbs"]
-        peak_note = f"copy bandwidth of {peaks['source']}"
-        r_unit = "GB/s"
-    value = world * work * args.steps / dev_total / scale
-    achieved = work / kernel_avg / scale
     line = {
-        "metric": {"attn": "int8 sliding-window attention prefill throughput",
-                   "attn_pv_fp8": "attention with fp8 P.V prefill throughput", "ffn_i8": "gated FFN forward throughput",
-                   "qkvg": "fused Q/KV projection throughput",
-                   "ffn_f8": "gated FFN forward throughput", "decode": "int8 decode attention KV-cache bandwidth",
-                   "rms_norm": "RMSNorm bandwidth", "block": "quantized block forward throughput"}[args.workload],
+        "metric": METRICS[args.workload],
         "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dev_total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": dev_total / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic (seeded N(0,1) values quantised to FixedI8 codes)",
-        "config": dict(w.config, sharding=f"{world} x per-GPU workload, (batch, head) / token-row units, no collective"),
-        "tokens_per_s": world * w.tokens * args.steps / dev_total,
-        "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
-                     "traffic": measured_traffic(args.workload, w.units), "peak_source": peak_note, "kernel_ms": kernel_avg * 1e3,
-                     "nominal_frac": achieved / (4500.0 if w.bound == "tensor" else 7700.0)},
+        "config": dict(w.config, sharding=(
+            f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path"
+            if strong else f"{world} x per-GPU workload, token-row units, no collective")),
+        "tokens_per_s": tokens_job * args.steps / dev_total,
+        "roofline": dict(roofline(w, achieved, dev_total, peaks, lib_peaks, args.workload), kernel_ms=kernel_avg * 1e3),
         "clocks": clocks,
         "gpu_launches": int(launches),
         "wall_ms_per_step": wall_total / args.steps * 1e3,
+        "attn_schedule": args.attn_schedule,
     }
-    if gather_ms is not None:
-        line["gather_ms"] = gather_ms
+    if gather is not None:
+        line["gather"] = gather
     if args.workload in ("attn", "attn_pv_fp8"):
-        line["reference_count_tops"] = world * w.ref_ops * args.steps / dev_total / 1e12
+        line["reference_count_tops"] = (w.ref_ops if strong else world * w.ref_ops) * args.steps / dev_total / 1e12
     if e2e is not None:
-        e2e["value"] = world * work / (e2e["ms_per_step"] * 1e-3) / scale
-        e2e["unit"] = unit
         line["e2e"] = e2e
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rate, sample = w.cpu_sample()
-        line["cpu_baseline"] = {"value": rate / scale, "unit": unit, "cores": os.cpu_count() or 1, "kind": "port",
-                                "sample": sample}
+
+    if rank == 0 and world == 1:
+        if args.workload == "attn":
+            try:
+                rk = w.ref_kernel_sample()
+                if rk is not None:
+                    line["ref_kernel_baseline"] = rk
+            except Exception as e:
+                line["ref_kernel_baseline"] = {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
+        if not args.no_cpu_baseline:
+            rate, sample = w.cpu_sample()
+            line["cpu_baseline"] = {"value": rate / scale, "unit": unit, "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": sample}
+            if args.workload == "attn":
+                ref = reference_cpu_attention()
+                if ref is not None:
+                    line["cpu_reference_model"] = ref
+
+    # ---- the other kernels of the path (N = 1, default workload) ----
+    if rank == 0 and world == 1 and args.workload == "attn" and not args.no_side_workloads and not args.shape:
+        del w
+        torch.cuda.empty_cache()
+        side = {}
+        for name in SIDE_WORKLOADS:
+            try:
+                sw = WORKLOADS[name](stream, dev, None)
+                n = run.steps_for(sw.step, 0.7)
+                d_total, k_avg, _, n_launch, clk = run.time_steps(sw.step, n, 3)
+                u, sc = ("TOPS", 1e12) if sw.bound == "tensor" else ("GB/s", 1e9)
+                work = sw.ops if sw.bound == "tensor" else sw.alg_bytes
+                side[name] = {"metric": METRICS[name], "value": work * n / d_total / sc, "unit": u, "steps": n,
+                              "ms_per_step": d_total / n * 1e3, "tokens_per_s": sw.tokens * n / d_total, "dtype": sw.dtype,
+                              "config": sw.config, "gpu_launches": n_launch, "clocks": clk,
+                              "roofline": roofline(sw, work / k_avg / sc, d_total, peaks, lib_peaks, name)}
+                del sw
+            except Exception as e:   # one workload must not cost the headline its line
+                side[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            torch.cuda.empty_cache()
+        line["workloads"] = side
+        line["library_peaks"] = lib_peaks
+
     if rank == 0:
         print(json.dumps(line), flush=True)
-    for t in timers:
-        t.destroy()
     stream.close()
     if world > 1:
         dist.destroy_process_group()

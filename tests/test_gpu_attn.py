@@ -234,3 +234,39 @@ def test_attention_from_host_matches_single_launch(stream):
         kern.launch_from_host(streams, t(q), h_kv, tsk, tsv, tt, d_q, d_kv, d_out, h_out, None, W)
     for st in extra:
         st.close()
+
+
+@pytest.mark.parametrize("B,H,D,S,W", [(1, 2, 128, 512, 128), (2, 2, 64, 384, 0)])
+def test_attention_pv_fp8_against_the_int8_kernel(stream, B, H, D, S, W):
+    """The fp8 P.V kernel tied to the int8 kernel, which the reference's own kernel pins: with V drawn from small
+    integers (exact as int8 codes and as e4m3 values alike) both kernels normalise the same sum of p * v; they
+    differ only in how they quantise p (steps of 1/255 against eight-step e4m3 binades) and in the last rounding
+    (int8 code against bf16). So out_fp8 / v_scale stays within one code of the int8 kernel's output everywhere and
+    within a fraction of a code on average; a wrong V layout, scale, sink or normaliser would break this at once."""
+    from x17ai_b200 import kernels as K
+    rng = np.random.default_rng(B + H + D + S + W + 1)
+    q, kv, sk, _, temp = _inputs(rng, B, S, H, D)
+    v_int = rng.integers(-12, 13, (B, S, H, D)).astype(np.int8)
+    sv_int = rng.integers(-12, 13, (H, D)).astype(np.int8)
+    kv4 = kv.reshape(B, S, H, 2, D).copy()
+    kv4[:, :, :, 1, :] = v_int
+    kv_i8 = kv4.reshape(B, S, 2 * H * D)
+    out_i8, l_i8 = _launch(stream, q, kv_i8, sk, sv_int, temp, H, D, W)
+    # the same values as e4m3 bytes, with a per-head scale that the output must carry
+    kv4[:, :, :, 1, :] = formats.hw_f32_to_e4m3(v_int.astype(np.float32)).view(np.int8)
+    assert np.array_equal(formats.hw_e4m3_to_f32(kv4[:, :, :, 1, :].view(np.uint8)), v_int.astype(np.float32))
+    sv8 = formats.hw_f32_to_e4m3(sv_int.astype(np.float32))
+    v_scale = (0.5 + rng.random(H)).astype(np.float32)
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    tq, tkv, tsk, tsv, tt, tvs = t(q), t(kv4.reshape(B, S, 2 * H * D)), t(sk), t(sv8), t(temp), t(v_scale)
+    out = torch.zeros((B, S, H * D), dtype=torch.bfloat16, device="cuda")
+    l = torch.zeros((B, H, S), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    kern.launch_pv_fp8(stream, tq, tkv, tsk, tsv, tt, tvs, out, l, W)
+    stream.synchronize()
+    got = out.float().cpu().numpy().reshape(B, S, H, D) / v_scale[None, None, :, None]
+    diff = np.abs(got - out_i8.reshape(B, S, H, D).astype(np.float32))
+    assert diff.max() <= 1.0 and diff.mean() <= 0.3, (diff.max(), diff.mean())
+    # the normaliser: L = log2(scale * sum) + max with scale 256 here and 255 there
+    assert np.max(np.abs(l.cpu().numpy() - l_i8 - np.log2(256.0 / 255.0))) <= 1e-3

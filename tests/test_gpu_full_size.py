@@ -67,6 +67,42 @@ def test_attention_prefill_full_size(stream):
     assert not torch.equal(out1[0, :S // 2], out[3, :S // 2])
 
 
+def test_attention_pv_fp8_full_size(stream):
+    """configs[2]: the fp8 P.V variant at batch 8, 32 heads x 128, 8192 tokens, window 1024; sampled (sequence,
+    head) units against the oracle of this mode (bf16 output within 1e-2 x RMS), and a sequence launched alone
+    returns the bytes it got inside the batch."""
+    from oracle import formats
+    from x17ai_b200 import kernels as K
+    B, H, D, S, W = 8, 32, 128, 8192, 1024
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, kv, sk = _codes(g, B, S, H * D), _codes(g, B, S, 2 * H * D), _codes(g, H, D)
+    kv.view(B, S, H, 2, D)[:, :, :, 1, :] = torch.randn(B, S, H, D, generator=g, device="cuda").to(torch.float8_e4m3fn).view(torch.int8)
+    sv8 = torch.randn(H, D, generator=g, device="cuda").to(torch.float8_e4m3fn).view(torch.uint8)
+    temp = (0.5 + torch.rand(H, generator=g, device="cuda")).float()
+    v_scale = (0.25 + torch.rand(H, generator=g, device="cuda")).float()
+    out = torch.zeros(B, S, H * D, dtype=torch.bfloat16, device="cuda")
+    l = torch.zeros(B, H, S, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    kern.launch_pv_fp8(stream, q, kv, sk, sv8, temp, v_scale, out, l, W)
+    stream.synchronize()
+    for b, h in ((0, 3), (6, 30)):
+        qh = q[b, :, h * D:(h + 1) * D].cpu().numpy()
+        kh = kv[b, :, 2 * h * D:2 * h * D + D].cpu().numpy()
+        vh = kv[b, :, 2 * h * D + D:2 * (h + 1) * D].cpu().numpy().view(np.uint8)
+        ref, ref_l = o_attn.attn_fwd_pv_fp8(qh, kh, vh, sk[h:h + 1].cpu().numpy(), sv8[h:h + 1].cpu().numpy(),
+                                            temp[h:h + 1].cpu().numpy(), v_scale[h:h + 1].cpu().numpy(), W, 1, D)
+        got = out[b, :, h * D:(h + 1) * D].float().cpu().numpy()
+        rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+        assert np.max(np.abs(got - ref)) <= 1e-2 * rms + 2.0 ** -8 * np.abs(ref).max(), (b, h)
+        assert np.max(np.abs(l[b, h].cpu().numpy() - ref_l[0])) <= 1e-3
+    out1 = torch.zeros(1, S, H * D, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    kern.launch_pv_fp8(stream, q[5:6], kv[5:6], sk, sv8, temp, v_scale, out1, None, W)
+    stream.synchronize()
+    assert torch.equal(out1[0], out[5])
+
+
 def test_ffn_full_size(stream):
     """configs[3]: 16384 tokens, d_model 4096, hidden 14336: GeGLU GEMM and the e4m3 x int8 projection with the
     gated residual, sampled token rows against the oracle (rows are independent units)."""

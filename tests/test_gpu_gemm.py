@@ -212,3 +212,31 @@ def test_gemm_argument_errors(stream):
     c = torch.zeros((128, 256), dtype=torch.int8, device="cuda")
     with pytest.raises(X17Error, match="gemm input b has 128 columns, but should have 256"):
         k.launch(stream, a, b, c)
+
+
+def test_ffn_e4m3_weights_and_activations(stream):
+    """The FFN with e4m3 weights and e4m3 activations under per-tensor scales (the benchmark description's second
+    FFN run; no reference implementation, so the oracle's restatement is the only pin): both GEMMs on the fp8
+    tensor path, GeGLU and gated-residual epilogues as in the int8 run."""
+    from x17ai_b200 import kernels as K
+    rng = np.random.default_rng(21)
+    M, Dm, F = 256, 512, 1024
+    xv = rng.standard_normal((M, Dm)).astype(np.float32)
+    x8, sx = o_gemm.quantize_e4m3_per_tensor(xv)
+    x_i8 = formats.quantize_fixedi8(xv)
+    wf8, swf = o_gemm.quantize_e4m3_per_tensor(rng.standard_normal((2 * F, Dm)) * 0.02)
+    wy8, swy = o_gemm.quantize_e4m3_per_tensor(rng.standard_normal((2 * Dm, F)) * 0.02)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    f = torch.empty((M, F), dtype=torch.uint8, device="cuda")
+    y = torch.empty((M, Dm), dtype=torch.uint8, device="cuda")
+    tx8, twf, twy, txi = t(x8), t(wf8), t(wy8), t(x_i8)
+    torch.cuda.synchronize()
+    K.GemmKernel(K.ffn_f_fwd_e4m3_config(Dm, F, sx, swf)).launch(stream, tx8, twf, f)
+    K.GemmKernel(K.ffn_y_fwd_e4m3_config(F, Dm, swy)).launch(stream, f, twy, y, residual=txi)
+    stream.synchronize()
+    f_ref = o_gemm.ffn_f_fwd_e4m3(x8, sx, wf8, swf)
+    got_f = f.cpu().numpy()
+    assert (got_f != f_ref).mean() <= 2e-3
+    assert np.abs(formats.e4m3_to_f32(got_f)).mean() > 0.01    # the scales put the activations in e4m3's range
+    y_ref = o_gemm.ffn_y_fwd_e4m3(got_f, wy8, swy, x_i8)          # on the tensor the device fed the second GEMM
+    assert (y.cpu().numpy() != y_ref).mean() <= 2e-3

@@ -144,6 +144,39 @@ class AttnKernel:
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
             _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
 
+    def launch_head_block(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, head_begin):
+        """A head-sharded launch: this kernel's `n_heads` heads starting at head `head_begin` of wider tensors.
+        The reference kernel addresses a head group the same way, by column offset with explicit row strides
+        (cuda/attn_fwd_i8.cuh:378-384). `q` [.., S, q_stride] and `kv` [.., S, kv_stride] are the full-width
+        tensors of all heads, `sink_k` / `sink_v` [H_total, D] and `attn_temperature` [H_total] those of all
+        heads; `out` [.., S, o_stride] and `l` [.., n_heads, S] belong to this block alone (column 0 of `out`
+        is the block's first head)."""
+        c = self.config
+        batch = q.shape[0] if q.dim() == 3 else 1
+        q2, kv2, out2 = (q[0], kv[0], out[0]) if q.dim() == 3 else (q, kv, out)
+        seq_len, _ = matrix_shape("attention", "q", q2, (None, c.q_stride), DTYPE_INT8)
+        matrix_shape("attention", "kv", kv2, (seq_len, c.kv_stride), DTYPE_INT8)
+        total = sink_k.shape[0]
+        if head_begin < 0 or head_begin + c.n_heads > total:
+            raise X17Error(f"attention head block [{head_begin}, {head_begin + c.n_heads}) lies outside the {total} heads")
+        if (head_begin + c.n_heads) * c.head_dim > c.q_stride or 2 * (head_begin + c.n_heads) * c.head_dim > c.kv_stride:
+            raise X17Error("attention head block lies outside the q / kv row")
+        matrix_shape("attention", "sink_k", sink_k, (total, c.head_dim), DTYPE_INT8)
+        matrix_shape("attention", "sink_v", sink_v, (total, c.head_dim), DTYPE_INT8)
+        vector_shape("attention", "attn_temperature", attn_temperature, total, DTYPE_F32)
+        matrix_shape("attention", "out", out2, (seq_len, c.o_stride), DTYPE_INT8)
+        if l is not None:
+            matrix_shape("attention", "l", l[0] if l.dim() == 3 else l, (c.n_heads, seq_len), DTYPE_F32)
+        for t in (q, kv, out):
+            if not t.is_contiguous():
+                raise X17Error("attention batched inputs must be contiguous")
+        cfg = c._c()
+        hb, d = head_begin, c.head_dim
+        check(self._lib.x17ai_b200_attn_fwd_i8(
+            stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q) + hb * d, _ptr(kv) + 2 * hb * d,
+            _ptr(sink_k) + hb * d, _ptr(sink_v) + hb * d, _ptr(attn_temperature) + 4 * hb, _ptr(out), _ptr(l),
+            window_size))
+
     def launch_from_host(self, streams, h_q, h_kv, sink_k, sink_v, attn_temperature, q, kv, out, h_out,
                          l=None, window_size=0):
         """Batched attention whose q, kv arrive from and whose out returns to pinned host memory.
@@ -358,6 +391,23 @@ def ffn_f_fwd_config(model_dim, f_width):
 def ffn_y_fwd_f8_config(f_width, model_dim, b_dtype=DTYPE_INT8, c_dtype=DTYPE_E4M3):
     return GemmConfig(DTYPE_E4M3, b_dtype, c_dtype, EPI_RESIDUAL, f_width, 2 * model_dim,
                       inp_scale=math.sqrt(GELU_VAR_FIX_2 / f_width) / 8.0, out_scale=1.0)
+
+
+def ffn_f_fwd_e4m3_config(model_dim, f_width, x_scale, w_scale):
+    """GeGLU FFN input projection with e4m3 activations and e4m3 weights, one f32 scale per tensor (value =
+    scale * e4m3): the benchmark description's second FFN run; the reference has no such kernel (its "f8" GEMM,
+    gemm_b16.cuh:72-185, keeps int8 weights). The tensor scales are the epilogue's input scale: the
+    pre-activations are the plain products of the values (weights drawn N(0, 0.02) carry their own
+    1/sqrt(fan-in); the reference's Dm^-1/2 belongs to its unit-variance FixedI8 weights)."""
+    return GemmConfig(DTYPE_E4M3, DTYPE_E4M3, DTYPE_E4M3, EPI_GEGLU, model_dim, 2 * f_width,
+                      inp_scale=float(x_scale) * float(w_scale), out_scale=1.0)
+
+
+def ffn_y_fwd_e4m3_config(f_width, model_dim, w_scale, c_dtype=DTYPE_E4M3):
+    """FFN output projection of the same run: e4m3 GeGLU output x e4m3 weights (scale w_scale), gated residual
+    with the FixedI8 residual stream."""
+    return GemmConfig(DTYPE_E4M3, DTYPE_E4M3, c_dtype, EPI_RESIDUAL, f_width, 2 * model_dim,
+                      inp_scale=float(w_scale), out_scale=1.0)
 
 
 def ffn_y_fwd_i8_config(f_width, model_dim, c_dtype=DTYPE_INT8):
