@@ -375,6 +375,8 @@ typedef struct x17ai_GemmObjectDesc {
 	uint64_t c_stride, resid_stride;
 	float k0, k1, k2, k3, k4;
 	uint32_t smem_bytes, threads, m_per_block, n_per_block;
+	uint32_t k_a;      /* e4m3 x int8 objects: K of the activations (k is then 2 * k_a: two weight planes); else 0 */
+	uint32_t reserved;
 	uint8_t map_a[128], map_b[128];
 } x17ai_GemmObjectDesc;
 x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stream, x17ai_GemmConfig const *cfg,
@@ -390,6 +392,14 @@ typedef struct x17ai_AttnObjectDesc {
 } x17ai_AttnObjectDesc;
 x17ai_DiagnosticBuffer *x17ai_b200_attn_object_desc(x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg,
                                                     x17ai_AttnObjectDesc *desc);
+
+/* The four status words of a kernel object (a module loaded with x17ai_cuda_load_module whose cubin exports
+ * `x17_status`): synchronises the stream, copies them (0 = ok; else code << 16 | detail of the first bounded wait
+ * that ran out, or code 15 = an e4m3 x int8 GEMM object launched before its `prepare` entry point ran for the
+ * weights it was given; the reporting block; the number of reports; reserved) and clears them. The reference's
+ * kernels report nothing (cpp/cuda_shim.cpp:929-987 only reports launch failures); no counterpart there. */
+x17ai_DiagnosticBuffer *x17ai_b200_object_status(x17ai_CudaStreamHandle *stream, x17ai_CudaModuleHandle *module,
+                                                 uint32_t status[4]);
 
 /* Device-side status of the kernels launched so far on the stream's device: synchronises the
  * stream, copies the four status words (0 = ok; else code << 16 | detail of the first bounded

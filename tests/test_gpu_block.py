@@ -242,3 +242,9 @@ def test_block_through_kernel_objects(stream, name):
     for k in want:
         assert torch.equal(got[k], want[k]), k
     assert np.array_equal(got["q"].cpu().numpy(), g["q_i8"].reshape(S, H * D))
+    # six of six launches ran on kernel objects, and none of them gave up a wait
+    from x17ai_b200 import kernel_objects as KO
+    objs = [obj.k_q, obj.k_kv, obj.k_attn, obj.k_attn_y, obj.k_ffn_f, obj.k_ffn_y]
+    assert all(isinstance(o, (KO.GemmObject, KO.AttnObject)) for o in objs)
+    for o in objs:
+        assert o.kernel.status(stream) == [0, 0, 0, 0]

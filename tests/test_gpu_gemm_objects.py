@@ -67,6 +67,50 @@ def test_gemm_objects_on_fixtures(stream, name):
     both(K.attn_y_fwd_config(hd, Dm), "attn_y", ao, wy, (S, Dm), torch.uint8, residual=x)
 
 
+@pytest.mark.parametrize("name", ["block_d64_w64", "block_d128_w128", "block_d32_w0"])
+def test_e4m3_x_int8_object_on_fixtures(stream, name):
+    """The sixth kernel of the reference's block (ffn_y_fwd_f8, src/main.rs:620-675) as a kernel object: launched
+    with the reference's argument list (e4m3 activations, the int8 weights, the FixedI8 residual) after one
+    `prepare` launch for those weights, it returns the bytes of the library's entry point, which takes the split
+    planes; before `prepare` it computes nothing and says so in its status words."""
+    from x17ai_b200 import kernel_objects, kernels as K
+    g, c = load_golden(name)
+    S, Dm, F = c["S"], c["Dm"], c["F"]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    x, f, wy = t(g["x_i8"].reshape(S, Dm)), t(g["ffn_f_f8"].reshape(S, F)), t(g["ffn_y_weights_i8"].reshape(2 * Dm, F))
+    cfg = K.ffn_y_fwd_f8_config(F, Dm)
+    want = torch.zeros(S, Dm, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    K.GemmKernel(cfg).launch(stream, f, K.split_i8_weights(stream, wy), want, residual=x)
+    stream.synchronize()
+
+    obj = kernel_objects.GemmObject(stream, cfg, f"ffn_y_f8_{name}")
+    m = obj.kernel.meta
+    p = lambda v: ctypes.c_void_p(v.data_ptr())
+    got = torch.full((S, Dm), 7, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    grid = (max(1, S // m["M_PER_BLOCK"]), max(1, 2 * Dm // m["N_PER_BLOCK"]), 1)
+    args = (p(f), ctypes.c_uint64(S), p(wy), ctypes.c_uint64(2 * Dm), p(got), p(x))
+    # launched cold, as the reference's host would without the set-up launch: refused, nothing written
+    obj.kernel.launch(stream, grid, (m["THREADS_PER_BLOCK"], 1, 1), m["SMEM_BYTES"], *args)
+    st = obj.kernel.status(stream)
+    assert st[0] >> 16 == 15 and st[2] >= 1, st
+    assert bool((got == 7).all())
+    obj.prepare(stream, wy)
+    obj.kernel.launch(stream, grid, (m["THREADS_PER_BLOCK"], 1, 1), m["SMEM_BYTES"], *args)
+    assert obj.kernel.status(stream) == [0, 0, 0, 0]
+    assert torch.equal(got, want)
+    # through the launcher (prepares by itself for a new weight tensor) and again for other weights
+    wy2 = t(np.ascontiguousarray(g["ffn_y_weights_i8"].reshape(2 * Dm, F)[::-1]))
+    got2, want2 = torch.zeros_like(got), torch.zeros_like(got)
+    torch.cuda.synchronize()
+    obj.launch(stream, f, wy2, got2, residual=x)
+    K.GemmKernel(cfg).launch(stream, f, K.split_i8_weights(stream, wy2), want2, residual=x)
+    stream.synchronize()
+    assert torch.equal(got2, want2) and obj.kernel.status(stream) == [0, 0, 0, 0]
+    obj.kernel.unload()
+
+
 def test_gemm_object_any_grid_and_reuse(stream):
     """The object strides over its tiles by the number of CTAs it was launched with: a single CTA, the
     reference's grid and a grid larger than the tile count give the same bytes; a second launch with other

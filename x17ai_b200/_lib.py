@@ -61,6 +61,7 @@ class GemmObjectDesc(Structure):
                 ("rrms_cols", c_uint32), ("c_stride", c_uint64), ("resid_stride", c_uint64),
                 ("k0", c_uint32), ("k1", c_uint32), ("k2", c_uint32), ("k3", c_uint32), ("k4", c_uint32),   # f32 bit patterns
                 ("smem_bytes", c_uint32), ("threads", c_uint32), ("m_per_block", c_uint32), ("n_per_block", c_uint32),
+                ("k_a", c_uint32), ("reserved", c_uint32),
                 ("map_a", c_uint8 * 128), ("map_b", c_uint8 * 128)]
 
 
@@ -120,6 +121,7 @@ SIGNATURES = {
     "x17ai_b200_split_i8_weights": (DIAG, [c_void_p, c_void_p, c_size_t, c_size_t, c_void_p]),
     "x17ai_b200_rms_norm": (DIAG, [c_void_p, c_int32, c_void_p, c_size_t, c_size_t, c_void_p, c_void_p, c_double]),
     "x17ai_b200_read_status": (DIAG, [c_void_p, POINTER(c_uint32)]),
+    "x17ai_b200_object_status": (DIAG, [c_void_p, c_void_p, POINTER(c_uint32)]),
     "x17ai_b200_take_diagnostic": (c_size_t, [DIAG, c_char_p, c_size_t]),
     "x17ai_b200_graph_begin": (DIAG, [c_void_p]),
     "x17ai_b200_graph_end": (DIAG, [c_void_p, POINTER(c_void_p)]),

@@ -61,9 +61,10 @@ class BlockForward:
         self.k_ffn_f = K.GemmKernel(K.ffn_f_fwd_config(c.model_dim, c.ffn_width))
         self.k_ffn_y = K.GemmKernel(K.ffn_y_fwd_f8_config(c.ffn_width, c.model_dim))
         if kernel_objects:
-            # the five kernels that exist as kernel objects (kernel.cubin + meta.json, launched through the
-            # generic load_module / get_kernel / launch_kernel with the reference's grids and arguments)
-            # in place of the library's entry points; the e4m3 x int8 projection has no object
+            # all six kernels as kernel objects (kernel.cubin + meta.json, launched through the generic
+            # load_module / get_kernel / launch_kernel with the reference's grids and arguments) in place of
+            # the library's entry points; the e4m3 x int8 projection's object keeps its own e4m3 planes of
+            # the int8 weights, made by one set-up launch
             if fused_qkv:
                 raise K.X17Error("kernel_objects and fused_qkv exclude each other (the fused projection has no kernel object)")
             from . import kernel_objects as KO
@@ -73,8 +74,14 @@ class BlockForward:
             self.k_attn_y = KO.GemmObject(stream, self.k_attn_y.config, f"attn_y_{tag}")
             self.k_ffn_f = KO.GemmObject(stream, self.k_ffn_f.config, f"ffn_f_{tag}")
             self.k_attn = KO.AttnObject(stream, self.k_attn.config, f"attn_{tag}")
-        # e4m3 activations x int8 weights run on the fp8 tensor path with the weights split once
-        self.w_ffn_y_split = K.split_i8_weights(stream, w_ffn_y)
+            self.k_ffn_y = KO.GemmObject(stream, self.k_ffn_y.config, f"ffn_y_f8_{tag}")
+        # e4m3 activations x int8 weights run on the fp8 tensor path with the weights split once (the kernel
+        # object does that itself from the int8 weights it is given)
+        if kernel_objects:
+            self.k_ffn_y.prepare(stream, w_ffn_y)
+            self.w_ffn_y_split = w_ffn_y
+        else:
+            self.w_ffn_y_split = K.split_i8_weights(stream, w_ffn_y)
         if fused_qkv:
             self.w_qkv = torch.cat((w_q, w_kv), dim=0).contiguous()
         stream.synchronize()

@@ -552,9 +552,9 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stre
 	if (desc == nullptr) return static_diag("x17ai_b200_gemm_object_desc(): null argument");
 	GemmPlan plan{};
 	if (auto *d = plan_gemm(cfg, &plan, who)) return d;
-	if (plan.f8) {
+	if (plan.f8 && !plan.split) {
 		return make_diag("x17ai_b200: unsupported kernel object", who,
-						 ": kernel objects exist for int8 x int8 GEMMs (the split e4m3 weight planes are not what the reference's host passes)");
+						 ": kernel objects exist for the int8 x int8 and the e4m3 x int8 GEMMs of the reference's block");
 	}
 	StreamScope scope(stream, who);   // the driver encodes tensor maps inside a context
 	if (scope.diag) return scope.diag;
@@ -578,12 +578,14 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stre
 	desc->threads = THREADS;
 	desc->m_per_block = BM;
 	desc->n_per_block = BN;
+	desc->k_a = plan.split ? p.k_a : 0;
 	// templates of the two tensor maps: shape, strides, box and swizzle are final, the base address and
 	// A's row count are written by the kernel object itself at launch
 	void *const dummy = reinterpret_cast<void *>(uintptr_t(1) << 20);
 	CUtensorMap ta, tb;
 	CUresult e = make_map_2d(&ta, dummy, cfg->a_cols, BM, cfg->a_cols, BK, BM);
-	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, dummy, cfg->a_cols, cfg->b_rows, cfg->a_cols, BK, BN);
+	// B: the int8 weights [N, K], or the object's own two e4m3 planes [N, 2K] of them
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, dummy, p.k, cfg->b_rows, p.k, BK, BN);
 	if (e != CUDA_SUCCESS) {
 		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who, ": cuTensorMapEncodeTiled failed: ",
 						 x17::cu_error_text(e));
@@ -591,6 +593,29 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stre
 	static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
 	std::memcpy(desc->map_a, &ta, 128);
 	std::memcpy(desc->map_b, &tb, 128);
+	return nullptr;
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_object_status(x17ai_CudaStreamHandle *stream, x17ai_CudaModuleHandle *module,
+												 uint32_t status[4]) {
+	char const *who = "x17ai_b200_object_status()";
+	if (module == nullptr || status == nullptr) return static_diag("x17ai_b200_object_status(): null argument");
+	StreamScope scope(stream, who);
+	if (scope.diag) return scope.diag;
+	CUdeviceptr ptr = 0;
+	size_t bytes = 0;
+	CUresult e = DRV(cuModuleGetGlobal)(&ptr, &bytes, reinterpret_cast<CUmodule>(module), "x17_status");
+	if (e != CUDA_SUCCESS || bytes < 4 * sizeof(uint32_t)) {
+		return make_diag("x17ai_b200: no status words", who, ": the module exports no x17_status words: ",
+						 x17::cu_error_text(e));
+	}
+	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+	cudaError_t ce = cudaStreamSynchronize(s);
+	if (ce == cudaSuccess) ce = cudaMemcpy(status, reinterpret_cast<void *>(ptr), 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+	if (ce == cudaSuccess) ce = cudaMemset(reinterpret_cast<void *>(ptr), 0, 4 * sizeof(uint32_t));
+	if (ce != cudaSuccess) {
+		return make_diag("x17ai_b200: status read failed", who, ": reading the status words failed: ", cudaGetErrorString(ce));
+	}
 	return nullptr;
 }
 

@@ -34,6 +34,7 @@
 	X(cuModuleLoad)               \
 	X(cuModuleUnload)             \
 	X(cuModuleGetFunction)        \
+	X(cuModuleGetGlobal)          \
 	X(cuFuncSetAttribute)         \
 	X(cuFuncGetAttribute)         \
 	X(cuLaunchKernel)             \

@@ -26,7 +26,7 @@ __constant__ MapBytes c_map_q = {{X17_MAP_Q}};
 __constant__ MapBytes c_map_kv = {{X17_MAP_KV}};
 __device__ MapBytes g_maps[256][SLOTS_PER_SM][2];
 __device__ unsigned g_next[256];
-__device__ unsigned g_status[4];
+
 
 __device__ __forceinline__ void map_set_address(unsigned smem_map, void const *ptr) {
 	asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"l"(
@@ -42,6 +42,10 @@ __device__ __forceinline__ void map_set_rows(unsigned smem_map, unsigned rows) {
 }
 
 }  // namespace
+
+extern "C" {
+__device__ unsigned x17_status[4];   // read by the host through cuModuleGetGlobal
+}
 
 extern "C" __global__ void __launch_bounds__(x17::attn_cfg::THREADS, 2)
 kernel(unsigned long long seq_len, signed char const *q, signed char const *kv, signed char const *sink_k,
@@ -105,7 +109,7 @@ kernel(unsigned long long seq_len, signed char const *q, signed char const *kv, 
 	p.o_batch_stride = 0;
 	p.l = l;
 	p.l_batch_stride = 0;
-	p.status = g_status;
+	p.status = x17_status;
 	constexpr u32 HEADS_PER_CTA = X17_HEAD_DIM >= 128 ? 1 : 128 / X17_HEAD_DIM;
 	for (u32 h = 0; h < HEADS_PER_CTA; ++h) {
 		u32 const head = blockIdx.y * HEADS_PER_CTA + h;

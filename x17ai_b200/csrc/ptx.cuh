@@ -36,6 +36,7 @@ enum StatusCode : u32 {
 	ST_WAIT_S_DONE = 6,
 	ST_WAIT_O_FULL = 7,
 	ST_WAIT_Q_FULL = 8,
+	ST_NOT_PREPARED = 15,  // a kernel object was launched before the set-up launch it needs
 };
 
 X17_DEV void report_status(u32 *status, u32 code, u32 detail) {

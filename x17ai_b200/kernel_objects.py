@@ -4,9 +4,10 @@ The reference's host renders a template per shape, compiles it with nvcc into a 
 `extern "C" kernel(...)`, runs a small program that prints launch metadata as JSON, loads the cubin
 through the shim and launches it with an array of pointers to the arguments
 (src/device/cuda/kernel_build.rs:38-134, cuda_shim.rs:464-489).  This module does the same for the
-RMSNorm kernel, the int8 x int8 GEMMs and the int8 attention; the tensor-core objects
-carry templates of their TMA tensor maps and finish them on the device with the pointers they are
-launched with.
+RMSNorm kernel, the int8 x int8 GEMMs, the e4m3 x int8 GEMM (ffn_y_fwd_f8) and the int8 attention; the
+tensor-core objects carry templates of their TMA tensor maps and finish them on the device with the pointers
+they are launched with. Every tensor-core object exports four status words (`x17_status`), read with
+CubinKernel.status().
 """
 import ctypes
 import json
@@ -48,8 +49,10 @@ def build_rms_norm(model_dim: int, eps: float = 2.0 ** -70, force: bool = False)
 
 
 def build_gemm(stream, config, name: str, force: bool = False) -> Path:
-    """One int8 x int8 GEMM configuration (a kernels.GemmConfig) as cache/kernels/<name>/kernel.cubin +
-    meta.json, the form GemmKernel::new produces in the reference (gemm.rs:368-443): the epilogue
+    """One GEMM configuration of the reference's block (a kernels.GemmConfig: int8 x int8, or e4m3 x int8 whose
+    object owns the two e4m3 planes of its weights and a `prepare` entry point that fills them) as
+    cache/kernels/<name>/kernel.cubin + meta.json, the form GemmKernel::new produces in the reference
+    (gemm.rs:368-443): the epilogue
     constants and templates of the two TMA tensor maps come from x17ai_b200_gemm_object_desc (the maps
     need the CUDA driver, so this runs where a GPU is), the kernel patches the maps with the pointers
     and row count it is launched with. Launch it as the reference does: grid
@@ -61,7 +64,7 @@ def build_gemm(stream, config, name: str, force: bool = False) -> Path:
     desc = _lib.GemmObjectDesc()
     cfg = config._c()
     check(_lib.load().x17ai_b200_gemm_object_desc(stream.handle, ctypes.byref(cfg), ctypes.byref(desc)))
-    fields = ("epilogue_kind", "n_raw", "k", "head_dim", "rrms_cols", "c_stride", "resid_stride", "k0", "k1", "k2", "k3", "k4")
+    fields = ("epilogue_kind", "n_raw", "k", "k_a", "head_dim", "rrms_cols", "c_stride", "resid_stride", "k0", "k1", "k2", "k3", "k4")
     key = json.dumps([int(getattr(desc, f)) for f in fields] + list(desc.map_a) + list(desc.map_b))
     stamp = d / "config.json"
     if (not force and cubin.exists() and meta.exists() and stamp.exists() and stamp.read_text() == key
@@ -75,6 +78,8 @@ def build_gemm(stream, config, name: str, force: bool = False) -> Path:
     defs = {"X17_EPI": desc.epilogue_kind, "X17_N_RAW": desc.n_raw, "X17_K": desc.k, "X17_HEAD_DIM": desc.head_dim,
             "X17_RRMS_COLS": desc.rrms_cols, "X17_C_STRIDE": desc.c_stride, "X17_RESID_STRIDE": desc.resid_stride,
             "X17_K0": desc.k0, "X17_K1": desc.k1, "X17_K2": desc.k2, "X17_K3": desc.k3, "X17_K4": desc.k4}
+    if desc.k_a:
+        defs.update({"X17_SPLIT": 1, "X17_K_A": desc.k_a})
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--ftz=true", "--fmad=true",
            "-include", str(maps)] + [f"-D{k}={int(v)}u" for k, v in defs.items()] + ["--cubin", "-o", str(cubin), str(src)]
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -135,11 +140,21 @@ class CubinKernel:
         check(self._lib.x17ai_cuda_read_kernel_attrs(self.kernel, ctypes.byref(attrs)))
         self.attrs = attrs
 
-    def launch(self, stream, grid, block, smem, *args):
+    def launch(self, stream, grid, block, smem, *args, kernel=None):
         """`args` are ctypes values; the shim receives an array of pointers to them, as the Rust host passes."""
         arr = (ctypes.c_void_p * len(args))(*[ctypes.cast(ctypes.pointer(a), ctypes.c_void_p) for a in args])
-        check(self._lib.x17ai_cuda_launch_kernel(stream.handle, self.kernel, grid[0], grid[1], grid[2],
+        check(self._lib.x17ai_cuda_launch_kernel(stream.handle, kernel or self.kernel, grid[0], grid[1], grid[2],
                                                  block[0], block[1], block[2], smem, arr))
+
+    def entry(self, name: str, smem: int = 0):
+        """Another entry point of the same module (x17ai_cuda_get_kernel)."""
+        return unwrap(self._lib.x17ai_cuda_get_kernel(self.module, name.encode(), smem))
+
+    def status(self, stream):
+        """The object's four status words (all zero = no bounded wait ran out, no refusal); reading clears them."""
+        st = (ctypes.c_uint32 * 4)()
+        check(self._lib.x17ai_b200_object_status(stream.handle, self.module, st))
+        return [int(v) for v in st]
 
     def unload(self):
         check(self._lib.x17ai_cuda_del_module(self.module))
@@ -150,15 +165,36 @@ class GemmObject:
     through the generic shim calls with the reference's grid and argument list (gemm.rs:591-641)."""
 
     def __init__(self, stream, config, name: str):
+        from . import kernels as K
         self.config = config
         self.kernel = CubinKernel(stream, build_gemm(stream, config, name))
+        # e4m3 activations x int8 weights: the object keeps two e4m3 planes of the weights, filled by `prepare`
+        self.split = config.a_dtype == K.DTYPE_E4M3 and config.b_dtype == K.DTYPE_INT8
+        self._prepare = self.kernel.entry("prepare") if self.split else None
+        self._prepared_for = None
+
+    def prepare(self, stream, b):
+        """The set-up launch of an e4m3 x int8 object: once per weight tensor (the reference's host would add this
+        one launch where it loads the weights)."""
+        from . import kernels as K
+        K.matrix_shape("gemm", "b", b, (self.config.b_rows, self.config.a_cols), K.DTYPE_INT8)
+        self.kernel.launch(stream, (296, 1, 1), (256, 1, 1), 0, ctypes.c_void_p(b.data_ptr()), ctypes.c_uint64(b.shape[0]),
+                           kernel=self._prepare)
+        self._prepared_for = b.data_ptr()
 
     def launch(self, stream, a, b, c, rrms=None, residual=None):
         from . import kernels as K
         m = self.kernel.meta
         # the same checks as GemmKernel.launch (tensor_check.rs:19-101, gemm.rs:591-641): a wrongly sized
         # output would be written out of bounds
-        K.GemmKernel(self.config).check_shapes(a, b, c, rrms, residual)
+        if self.split:
+            K.matrix_shape("gemm", "a", a, (None, self.config.a_cols), K.DTYPE_E4M3)
+            K.matrix_shape("gemm", "c", c, (a.shape[0], self.config.b_rows // 2), self.config.c_dtype)
+            K.matrix_shape("gemm", "residual", residual, (a.shape[0], self.config.b_rows // 2), K.DTYPE_INT8)
+            if self._prepared_for != b.data_ptr():
+                self.prepare(stream, b)
+        else:
+            K.GemmKernel(self.config).check_shapes(a, b, c, rrms, residual)
         ptr = lambda t: ctypes.c_void_p(t.data_ptr())
         args = [ptr(a), ctypes.c_uint64(a.shape[0]), ptr(b), ctypes.c_uint64(b.shape[0]), ptr(c)]
         if rrms is not None:
