@@ -208,6 +208,26 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
 	float const *attn_temperature, float const *v_scale, uint16_t *out_bf16, float *l, size_t window_size);
 
 /*
+ * The int8 attention for inputs quantised with one symmetric f32 scale per token and head (value = scale * code,
+ * scale = absmax / 127: the input format of the benchmark description) and bf16 output.  No counterpart in the
+ * reference, whose tensors carry one global FixedI8 scale (cuda/utils_b8.cuh:7-10, 629-632) and whose kernel writes
+ * FixedI8 (cuda/attn_fwd_i8.cuh:293-351); masks, sink token, temperature, maximum and normaliser are those of
+ * x17ai_b200_attn_fwd_i8, which this call equals for q_scale = k_scale = v_scale = 1/8 up to the output format
+ * (out = code / 8).  Q.K^T and P.V stay exact integer products on the int8 tensor path:
+ *   x[i][j] = (q_i . k_j)_int32 * q_scale[i] * k_scale[j] * D^-1/2 * log2(min(W', i) + 4) * temp_h
+ *   P[i][j] = rint(255 * 2^(x - m_i) * v_scale[j] / g_i),  g_i = max_j 2^(x - m_i) * v_scale[j]   (u8)
+ *   out[i]  = bf16((g_i / 255 * sum_j P[i][j] v_j + 2^(sink - m_i) * sink_v / 8) / sum_i),  sum_i as before
+ *   q_scale, k_scale, v_scale: f32 [batch][n_heads][seq_len];  sink_k, sink_v FixedI8 as before;
+ *   out bf16 [batch][seq_len][o_stride] (o_stride in elements);  l [batch][n_heads][seq_len] or NULL.
+ * Always the one-CTA-per-query-tile kernel.
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_scaled(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, float const *q_scale, int8_t const *kv, float const *k_scale, float const *v_scale,
+	int8_t const *sink_k, int8_t const *sink_v, float const *attn_temperature, uint16_t *out_bf16, float *l,
+	size_t window_size);
+
+/*
  * Which kernel the three attention entry points above and below launch.  No counterpart in the
  * reference (its one kernel, cuda/attn_fwd_i8.cuh:368-619, runs one CTA per 64 queries and head group):
  *   X17AI_B200_ATTN_PER_TILE (default, the faster one on configs[1]): one CTA per 128-query tile, two

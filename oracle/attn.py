@@ -232,3 +232,57 @@ def attn_fwd_pv_fp8(q, k, v_e4m3, sink_k, sink_v_e4m3, temperature, v_scale, win
         out[:, sl] = (o / total.astype(np.float64)[:, None] * float(v_scale[h])).astype(F32)
         l[h] = (np.log2(total) + m).astype(F32)
     return out, l
+
+
+def quantize_per_token(x):
+    """Symmetric int8 quantisation with one f32 scale per token and head (the benchmark description's input
+    format): x [..., D] -> (codes int8 [..., D], scale f32 [...]) with scale = absmax / 127, x ~ scale * code."""
+    x = np.asarray(x, dtype=np.float64)
+    amax = np.abs(x).max(axis=-1)
+    scale = np.where(amax > 0, amax / 127.0, 1.0).astype(F32)
+    codes = np.clip(np.rint(x / scale[..., None].astype(np.float64)), -127, 127).astype(np.int8)
+    return codes, scale
+
+
+def attn_fwd_i8_scaled(q, q_scale, k, k_scale, v, v_scale, sink_k, sink_v, temperature, window, quantise_p=True):
+    """The int8 attention on per-token-per-head scaled inputs with real-valued (bf16) output.  No counterpart in the
+    reference (one global FixedI8 scale, cuda/utils_b8.cuh:7-10); masks, sink, temperature, maximum and normaliser
+    follow the reference kernel as attn_head does (cuda/attn_fwd_i8.cuh:408-450, 489-517): parity of this mode is
+    pinned by this restatement only, and by its case q_scale = k_scale = v_scale = 1/8, which is attn_head.
+      q, k, v int8 [S, H, D]; q_scale, k_scale, v_scale f32 [H, S]; sink_k, sink_v int8 [H, D] (FixedI8, code / 8);
+      returns out f64 [S, H, D] (before the bf16 cast) and l f32 [H, S].
+    `quantise_p` models the kernel's u8 probabilities P = rint(255 * 2^(x - m) * v_scale / g), g the row's largest
+    2^(x - m) * v_scale; without it the result is the plain float64 softmax attention of the dequantised inputs."""
+    q = np.asarray(q, dtype=np.int8); k = np.asarray(k, dtype=np.int8); v = np.asarray(v, dtype=np.int8)
+    s_len, n_heads, d = q.shape
+    w = _round_window(window)
+    i = np.arange(s_len)[:, None]
+    j = np.arange(s_len)[None, :]
+    mask = j >= i
+    if w is not None:
+        mask |= j < i - w
+    out = np.zeros((s_len, n_heads, d), dtype=np.float64)
+    l = np.zeros((n_heads, s_len), dtype=F32)
+    for h in range(n_heads):
+        temp = row_temperature(s_len, d, window).astype(np.float64) * float(temperature[h])     # includes the 1/64
+        a_row = temp * 64.0 * q_scale[h].astype(np.float64)
+        acc = q[:, h].astype(np.int64) @ k[:, h].astype(np.int64).T
+        x = acc * a_row[:, None] * k_scale[h].astype(np.float64)[None, :]
+        x = np.where(mask, -np.inf, x)
+        sink_s = (q[:, h].astype(np.int64) @ np.asarray(sink_k[h], dtype=np.int64)) * a_row * 0.125
+        m = np.maximum(sink_s, x.max(axis=1))
+        e = np.exp2(x - m[:, None])
+        sink_e = np.exp2(sink_s - m)
+        total = e.sum(axis=1) + sink_e
+        vs = v_scale[h].astype(np.float64)
+        if quantise_p:
+            wgt = e * vs[None, :]
+            g = wgt.max(axis=1)
+            p8 = np.where(g[:, None] > 0, np.rint(255.0 * wgt / np.where(g > 0, g, 1.0)[:, None]), 0.0)
+            o = (p8 @ v[:, h].astype(np.float64)) * (g / 255.0)[:, None]
+        else:
+            o = (e * vs[None, :]) @ v[:, h].astype(np.float64)
+        o = o + sink_e[:, None] * (np.asarray(sink_v[h], dtype=np.float64) / 8.0)[None, :]
+        out[:, h] = o / total[:, None]
+        l[h] = (np.log2(255.0 * total) + m).astype(F32)
+    return out, l

@@ -270,3 +270,74 @@ def test_attention_pv_fp8_against_the_int8_kernel(stream, B, H, D, S, W):
     assert diff.max() <= 1.0 and diff.mean() <= 0.3, (diff.max(), diff.mean())
     # the normaliser: L = log2(scale * sum) + max with scale 256 here and 255 there
     assert np.max(np.abs(l.cpu().numpy() - l_i8 - np.log2(256.0 / 255.0))) <= 1e-3
+
+
+def _scaled_case(rng, B, S, H, D):
+    """N(0,1) q, k, v quantised with per-token-per-head scales (absmax / 127), as the benchmark description draws them."""
+    out = []
+    for _ in range(3):
+        codes, scale = o_attn.quantize_per_token(rng.standard_normal((B, S, H, D)))
+        out.append((codes, np.ascontiguousarray(scale.transpose(0, 2, 1))))     # scale [B, H, S]
+    sk = formats.quantize_fixedi8(rng.standard_normal((H, D)))
+    sv = formats.quantize_fixedi8(rng.standard_normal((H, D)) * 1.3)
+    temp = (0.5 + rng.random(H)).astype(np.float32)
+    return out, sk, sv, temp
+
+
+def _launch_scaled(stream, qs, ks, vs, sk, sv, temp, H, D, W):
+    from x17ai_b200 import kernels as K
+    (qc, qscale), (kc, kscale), (vc, vscale) = qs, ks, vs
+    B, S = qc.shape[0], qc.shape[1]
+    kv = np.concatenate((kc, vc), axis=-1).reshape(B, S, 2 * H * D)
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    args = [t(qc.reshape(B, S, H * D)), t(qscale), t(kv), t(kscale), t(vscale), t(sk), t(sv), t(temp)]
+    out = torch.zeros((B, S, H * D), dtype=torch.bfloat16, device="cuda")
+    l = torch.zeros((B, H, S), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    kern.launch_scaled(stream, *args, out, l, W)
+    stream.synchronize()
+    return out.float().cpu().numpy().reshape(B, S, H, D), l.cpu().numpy()
+
+
+@pytest.mark.parametrize("B,H,D,S,W", [
+    (1, 4, 64, 256, 64),       # the benchmark description's CPU-runnable case, seed 0
+    (2, 2, 128, 640, 256),
+    (1, 2, 32, 200, 48),       # ragged
+    (1, 2, 128, 512, 0),
+])
+def test_attention_per_token_scales_bf16_out(stream, B, H, D, S, W):
+    """Per-token-per-head scaled int8 inputs, bf16 output: max-abs error <= 1e-2 x RMS (the bar the benchmark description
+    sets for bf16 outputs) against the float64 restatement with the kernel's u8 probabilities, and within the
+    quantisation noise of those probabilities (a few percent of the RMS at a 48-key window, where every key carries
+    weight) of the plain float64 softmax attention of the dequantised inputs. Parity of this mode is pinned by the
+    oracle only."""
+    rng = np.random.default_rng(0 if (B, H, D, S, W) == (1, 4, 64, 256, 64) else B + H + D + S + W)
+    (qs, ks, vs), sk, sv, temp = _scaled_case(rng, B, S, H, D)
+    got, l = _launch_scaled(stream, qs, ks, vs, sk, sv, temp, H, D, W)
+    for b in range(B):
+        args = (qs[0][b], qs[1][b], ks[0][b], ks[1][b], vs[0][b], vs[1][b], sk, sv, temp, W)
+        ref_q, ref_l = o_attn.attn_fwd_i8_scaled(*args, quantise_p=True)
+        rms = np.sqrt(np.mean(ref_q ** 2))
+        assert np.max(np.abs(got[b] - ref_q)) <= 1e-2 * rms + 2.0 ** -8 * np.abs(ref_q).max()    # + one bf16 ulp
+        assert np.max(np.abs(l[b] - ref_l)) <= 1e-3
+        ref, _ = o_attn.attn_fwd_i8_scaled(*args, quantise_p=False)
+        assert np.max(np.abs(got[b] - ref)) <= 6e-2 * rms
+        assert np.sqrt(np.mean((got[b] - ref) ** 2)) <= 1e-2 * rms
+
+
+def test_attention_per_token_scales_reduce_to_fixedi8(stream):
+    """With every scale equal to 1/8 the mode is the FixedI8 kernel, which the reference's kernel pins: out = code / 8
+    to bf16 and quantisation precision, L equal."""
+    rng = np.random.default_rng(77)
+    B, H, D, S, W = 1, 2, 128, 384, 128
+    q, kv, sk, sv, temp = _inputs(rng, B, S, H, D)
+    out_i8, l_i8 = _launch(stream, q, kv, sk, sv, temp, H, D, W)
+    kv4 = kv.reshape(B, S, H, 2, D)
+    eighth = np.full((B, H, S), 0.125, dtype=np.float32)
+    got, l = _launch_scaled(stream, (q.reshape(B, S, H, D), eighth), (kv4[:, :, :, 0], eighth), (kv4[:, :, :, 1], eighth),
+                            sk, sv, temp, H, D, W)
+    want = out_i8.reshape(B, S, H, D).astype(np.float32) / 8.0
+    # the FixedI8 output is rounded to 1/8; the bf16 one carries the unrounded value: half a code plus bf16 precision
+    assert np.max(np.abs(got - want)) <= 0.5 / 8 + 2.0 ** -8 * np.abs(want).max() + 1e-3
+    assert np.max(np.abs(l - l_i8)) <= 1e-3

@@ -108,6 +108,8 @@ SIGNATURES = {
     "x17ai_b200_attn_meta": (DIAG, [POINTER(AttnConfig), POINTER(AttnMeta)]),
     "x17ai_b200_attn_fwd_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7 + [c_size_t]),
     "x17ai_b200_attn_fwd_pv_fp8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 8 + [c_size_t]),
+    "x17ai_b200_attn_fwd_i8_scaled": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
     "x17ai_b200_attn_fwd_i8_debug": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7
                                      + [c_size_t] + [c_void_p] * 3),
     "x17ai_b200_attn_decode_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_void_p, c_void_p, c_size_t,

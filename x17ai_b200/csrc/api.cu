@@ -188,12 +188,13 @@ uint32_t rounded_window(size_t window_size, size_t seq_len) {
 	return w >= seq_len ? 0xFFFFFFFFu : uint32_t(w);
 }
 
-template <bool DEBUG, bool FP8PV = false>
+template <bool DEBUG, bool FP8PV = false, bool SCALED = false>
 x17ai_DiagnosticBuffer *attn_launch(
 	char const *who, x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch,
 	size_t seq_len, int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
 	float const *temperature, void *out, float *l, size_t window_size, int32_t *dbg_s,
-	uint8_t *dbg_p, int32_t *dbg_o, float const *v_scale = nullptr) {
+	uint8_t *dbg_p, int32_t *dbg_o, float const *v_scale = nullptr, float const *tok_q = nullptr,
+	float const *tok_k = nullptr, float const *tok_v = nullptr) {
 	if (auto *d = check_attn_config(cfg, who)) return d;
 	if (batch == 0 || seq_len == 0) {
 		return make_diag("x17ai_b200: empty attention input", who, ": attention input q has zero size");
@@ -242,13 +243,16 @@ x17ai_DiagnosticBuffer *attn_launch(
 	p.l = l;
 	p.l_batch_stride = cfg->n_heads * seq_len;
 	p.v_scale = v_scale;
+	p.tok_q_scale = tok_q;
+	p.tok_k_scale = tok_k;
+	p.tok_v_scale = tok_v;
 	p.status = scope.state().status;
 	p.dbg_s = dbg_s;
 	p.dbg_p = dbg_p;
 	p.dbg_o = dbg_o;
 
 	cudaError_t ce;
-	if (g_attn_schedule.load(std::memory_order_relaxed) == X17AI_B200_ATTN_PERSISTENT) {
+	if (!SCALED && g_attn_schedule.load(std::memory_order_relaxed) == X17AI_B200_ATTN_PERSISTENT) {
 		// items = runs of consecutive query tiles of one (batch, head), dealt round-robin to one CTA per
 		// SM. Long runs pay the unfused maximum sweep of their first tile less often; short runs
 		// balance the SMs: halve the run while fewer than two items per SM come out.
@@ -296,11 +300,11 @@ x17ai_DiagnosticBuffer *attn_launch(
 			return cudaSuccess;
 		};
 		if (d == 128) {
-			ce = go(x17::attn_fwd_kernel<128, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<128>());
+			ce = go(x17::attn_fwd_kernel<128, DEBUG, FP8PV, SCALED>, x17::attn_cfg::smem_bytes<128>());
 		} else if (d == 64) {
-			ce = go(x17::attn_fwd_kernel<64, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<64>());
+			ce = go(x17::attn_fwd_kernel<64, DEBUG, FP8PV, SCALED>, x17::attn_cfg::smem_bytes<64>());
 		} else {
-			ce = go(x17::attn_fwd_kernel<32, DEBUG, FP8PV>, x17::attn_cfg::smem_bytes<32>());
+			ce = go(x17::attn_fwd_kernel<32, DEBUG, FP8PV, SCALED>, x17::attn_cfg::smem_bytes<32>());
 		}
 	}
 	if (ce != cudaSuccess) {
@@ -777,6 +781,17 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
 									reinterpret_cast<int8_t const *>(kv), sink_k,
 									reinterpret_cast<int8_t const *>(sink_v), attn_temperature, out_bf16, l,
 									window_size, nullptr, nullptr, nullptr, v_scale);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_scaled(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, float const *q_scale, int8_t const *kv, float const *k_scale, float const *v_scale,
+	int8_t const *sink_k, int8_t const *sink_v, float const *attn_temperature, uint16_t *out_bf16, float *l,
+	size_t window_size) {
+	if (!q_scale || !k_scale || !v_scale) return static_diag("x17ai_b200_attn_fwd_i8_scaled(): null scale tensor");
+	return attn_launch<false, false, true>("x17ai_b200_attn_fwd_i8_scaled()", stream, cfg, batch, seq_len, q, kv, sink_k,
+										   sink_v, attn_temperature, out_bf16, l, window_size, nullptr, nullptr, nullptr,
+										   nullptr, q_scale, k_scale, v_scale);
 }
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_debug(

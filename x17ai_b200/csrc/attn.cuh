@@ -42,6 +42,8 @@ struct AttnParams {
 	void *out;  // int8 FixedI8, or bf16 in the fp8 P.V mode
 	u64 o_stride, o_batch_stride;  // in elements of the output type
 	f32 const *v_scale;  // fp8 P.V mode: per-head scale of the e4m3 V values
+	// per-token-per-head scale mode: value = scale * code, [batch][head][seq] f32 each (null otherwise)
+	f32 const *tok_q_scale, *tok_k_scale, *tok_v_scale;
 	f32 *l;  // [batch][head][seq] or null
 	u64 l_batch_stride;
 	u32 *status;
@@ -146,6 +148,55 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 	}
 }
 
+// Per-token-per-head scale mode (the benchmark description's input format; the reference has one global FixedI8
+// scale, cuda/utils_b8.cuh:7-10): value = scale[token] * code for q, k and v. The scores carry a per-key factor,
+// x = acc * a_row * k_scale[key], and V's per-key scale goes into the quantised probabilities:
+// P = rint(255 * 2^(x - m) * v_scale[key] / g), g = max over the row's keys of 2^(x - m) * v_scale[key], so that
+// P.V stays an exact u8 x s8 product and out = O * g / (255 * sum). These two helpers are the maximum sweep
+// (row maximum m of x, and of z = x + log2 v_scale) and the probability sweep of 32 columns.
+template <bool EDGE>
+X17_DEV void scaled_extreme_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 seq_len, f32 a_row, f32 const *ksc,
+								  f32 const *vsc, u32 lo, u32 span, f32 &m_loc, f32 &z_loc) {
+#pragma unroll
+	for (u32 i = 0; i < 32; ++i) {
+		u32 const key = key0 + i;
+		bool vis = key < seq_len;
+		if constexpr (EDGE) vis = vis && (col0 + i - lo) < span;
+		if (vis) {
+			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[i])), a_row), __ldg(ksc + key));
+			m_loc = fmaxf(m_loc, x);
+			z_loc = fmaxf(z_loc, __fadd_rn(x, lg2_approx(__ldg(vsc + key))));
+		}
+	}
+}
+template <bool EDGE>
+X17_DEV void scaled_softmax_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 seq_len, f32 a_row, f32 const *ksc,
+								  f32 const *vsc, f32 neg_m, f32 rg, u32 lo, u32 span, f32 &sum, u32 (&pk)[8]) {
+	using namespace attn_cfg;
+#pragma unroll
+	for (u32 g = 0; g < 8; ++g) {
+		u32 q4[4];
+#pragma unroll
+		for (u32 e4 = 0; e4 < 4; ++e4) {
+			u32 const i = 4 * g + e4;
+			u32 const key = key0 + i;
+			bool vis = key < seq_len;
+			if constexpr (EDGE) vis = vis && (col0 + i - lo) < span;
+			f32 pq = 0.0f;
+			if (vis) {
+				f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[i])), a_row), __ldg(ksc + key));
+				f32 const e = ex2_approx(__fadd_rn(x, neg_m));
+				sum = __fadd_rn(sum, e);
+				pq = fminf(__fmul_rn(__fmul_rn(e, __ldg(vsc + key)), rg), 255.0f);
+			}
+			q4[e4] = __float_as_uint(__fadd_rn(pq, MAGIC));   // rint(pq) in the low byte
+		}
+		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
+		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
+		pk[g] = __byte_perm(lo2, hi2, 0x5410);
+	}
+}
+
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
 // accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
 // The tensor maps are reached through pointers: kernel parameters for the library's entry points, maps
@@ -153,9 +204,10 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 // works on; the body may be called again by the same CTA for another head (it invalidates its
 // barriers and frees its TMEM columns before it returns) provided `more_calls` was set on the earlier
 // calls: a CTA that has given up its TMEM allocation permit must not allocate again.
-template <u32 D, bool DEBUG, bool FP8PV = false>
+template <u32 D, bool DEBUG, bool FP8PV = false, bool SCALED = false>
 X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv_ptr, AttnParams const &p, u32 head,
 						   bool more_calls = false) {
+	static_assert(!(SCALED && (FP8PV || DEBUG)), "the per-token-scale mode has no fp8 and no validation form");
 	using namespace attn_cfg;
 	static_assert(D == 32 || D == 64 || D == 128, "head_dim must be 32, 64 or 128");
 	constexpr u32 TILE_BYTES = BKV * D;
@@ -377,7 +429,14 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		f32 const head_t = __ldg(p.temperature + head);
 		f32 const temp = __fmul_rn(row_t, head_t);
 		bool const pos_t = head_t >= 0.0f;  // uniform over the CTA; row_t > 0 always
-		f32 const sink_s = __fmul_rn(__int2float_rn(sink_dot), temp);
+		// per-token-scale mode: x = acc * a_row * k_scale[key]; the FixedI8 mode is its case q_scale = k_scale = 1/8
+		u64 const tok_base = (u64(batch) * p.n_heads + head) * p.seq_len;
+		f32 const a_row = SCALED ? __fmul_rn(__fmul_rn(temp, 64.0f), row_ok ? __ldg(p.tok_q_scale + tok_base + qi) : 0.125f) : 0.0f;
+		f32 const *const ksc = SCALED ? p.tok_k_scale + tok_base : nullptr;
+		f32 const *const vsc = SCALED ? p.tok_v_scale + tok_base : nullptr;
+		// the sink key and value are FixedI8 (scale 1/8) in every mode
+		f32 const sink_s = SCALED ? __fmul_rn(__fmul_rn(__int2float_rn(sink_dot), a_row), 0.125f)
+								  : __fmul_rn(__int2float_rn(sink_dot), temp);
 
 		// the head's sink values as f32, once per CTA (read in the epilogue, two named barriers later)
 		if (threadIdx.x - 64u < D) {
@@ -401,6 +460,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		i32 ext[4];
 #pragma unroll
 		for (u32 i = 0; i < 4; ++i) ext[i] = pos_t ? INT32_MIN : INT32_MAX;
+		f32 m_loc = -INFINITY, z_loc = -INFINITY;  // per-token-scale mode
 		#pragma unroll 1
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			u32 const b = (t - t_begin) & 1u;
@@ -423,7 +483,15 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
-			if (edge) {
+			if constexpr (SCALED) {
+				if (edge) {
+					scaled_extreme_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+					scaled_extreme_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+				} else {
+					scaled_extreme_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+					scaled_extreme_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+				}
+			} else if (edge) {
 				if (pos_t) {
 					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
 					extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
@@ -459,10 +527,23 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 								: min(min(ext[0], ext[1]), min(ext[2], ext[3]));
 			if (e != (pos_t ? INT32_MIN : INT32_MAX)) cand = __fmul_rn(__int2float_rn(e), temp);
 		}
+		if constexpr (SCALED) cand = m_loc;
 		xchg[xid] = cand;
 		named_barrier_sync(1, ROW_THREADS);
 		f32 const m = fmaxf(sink_s, fmaxf(cand, xchg[xpartner]));
 		named_barrier_sync(1, ROW_THREADS);  // the exchange area is reused for the sums
+		// per-token-scale mode: g = 2^(mz - m), the largest 2^(x - m) * v_scale of the row; P = 255 * (...) / g
+		f32 g_row = 0.0f, rg = 0.0f;
+		if constexpr (SCALED) {
+			xchg[xid] = z_loc;
+			named_barrier_sync(1, ROW_THREADS);
+			f32 const mz = fmaxf(z_loc, xchg[xpartner]);
+			named_barrier_sync(1, ROW_THREADS);
+			if (mz > -INFINITY) {
+				g_row = ex2_approx(__fsub_rn(mz, m));
+				rg = __fmul_rn(255.0f, ex2_approx(__fsub_rn(m, mz)));
+			}
+		}
 
 		// ---- sweep 2: probabilities against the final maximum ----
 		f32 const neg_m = -m;
@@ -490,7 +571,15 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
 			u32 pk0[8], pk1[8];
-			if (edge) {
+			if constexpr (SCALED) {
+				if (edge) {
+					scaled_softmax_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
+					scaled_softmax_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
+				} else {
+					scaled_softmax_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
+					scaled_softmax_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
+				}
+			} else if (edge) {
 				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
 				softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			} else {
@@ -564,6 +653,21 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 						dst[0] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
 						dst[1] = make_uint4(o2[4], o2[5], o2[6], o2[7]);
 					}
+				} else if constexpr (SCALED) {
+					// O = (255 / g) * sum of 2^(x - m) * v; the sink's value is FixedI8 (code / 8); out = bf16(value)
+					f32 const ws8 = __fmul_rn(w_sink, 0.125f);
+					u32 o2[8];
+#pragma unroll
+					for (u32 i = 0; i < 16; i += 2) {
+						f32 const oa = __fmul_rn(__fmaf_rn(ws8, sv[i], __fmul_rn(__int2float_rn(i32(r[i])), g_row)), recip);
+						f32 const ob = __fmul_rn(__fmaf_rn(ws8, sv[i + 1], __fmul_rn(__int2float_rn(i32(r[i + 1])), g_row)), recip);
+						o2[i / 2] = cvt_bf16x2(oa, ob);
+					}
+					if (row_ok) {
+						uint4 *dst = reinterpret_cast<uint4 *>(static_cast<u16 *>(p.out) + out_off + c);
+						dst[0] = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+						dst[1] = make_uint4(o2[4], o2[5], o2[6], o2[7]);
+					}
 				} else {
 					// rint(clamp(o * recip)) through the 1.5 * 2^23 trick: the code is the low byte
 					u32 pk[4];
@@ -611,11 +715,11 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 	}
 }
 
-template <u32 D, bool DEBUG, bool FP8PV = false>
+template <u32 D, bool DEBUG, bool FP8PV = false, bool SCALED = false>
 __global__ void __launch_bounds__(attn_cfg::THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
 				const AttnParams p) {
-	attn_fwd_body<D, DEBUG, FP8PV>(&tm_q, &tm_kv, p, blockIdx.y);
+	attn_fwd_body<D, DEBUG, FP8PV, SCALED>(&tm_q, &tm_kv, p, blockIdx.y);
 }
 
 }  // namespace x17

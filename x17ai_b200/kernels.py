@@ -221,6 +221,33 @@ class AttnKernel:
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
             _ptr(attn_temperature), _ptr(v_scale), _ptr(out), _ptr(l), window_size))
 
+    def launch_scaled(self, stream, q, q_scale, kv, k_scale, v_scale, sink_k, sink_v, attn_temperature, out, l=None,
+                      window_size=0):
+        """Inputs with one f32 scale per token and head (value = scale * code; `q_scale`, `k_scale`, `v_scale`
+        f32 [B, H, S] or [H, S]), bf16 output: x17ai_b200_attn_fwd_i8_scaled."""
+        c = self.config
+        batch = q.shape[0] if q.dim() == 3 else 1
+        q2, kv2, out2 = (q[0], kv[0], out[0]) if q.dim() == 3 else (q, kv, out)
+        seq_len, _ = matrix_shape("attention", "q", q2, (None, c.q_stride), DTYPE_INT8)
+        matrix_shape("attention", "kv", kv2, (seq_len, c.kv_stride), DTYPE_INT8)
+        matrix_shape("attention", "sink_k", sink_k, (c.n_heads, c.head_dim), DTYPE_INT8)
+        matrix_shape("attention", "sink_v", sink_v, (c.n_heads, c.head_dim), DTYPE_INT8)
+        vector_shape("attention", "attn_temperature", attn_temperature, c.n_heads, DTYPE_F32)
+        matrix_shape("attention", "out", out2, (seq_len, c.o_stride), DTYPE_BF16)
+        for name, t in (("q_scale", q_scale), ("k_scale", k_scale), ("v_scale", v_scale)):
+            t2 = t[0] if t.dim() == 3 else t
+            if t.dim() == 3 and t.shape[0] != batch:
+                raise X17Error(f"attention input {name} must share the batch dimension")
+            matrix_shape("attention", name, t2, (c.n_heads, seq_len), DTYPE_F32)
+            if not t.is_contiguous():
+                raise X17Error(f"attention input {name} must be contiguous")
+        if l is not None:
+            matrix_shape("attention", "l", l[0] if l.dim() == 3 else l, (c.n_heads, seq_len), DTYPE_F32)
+        cfg = c._c()
+        check(self._lib.x17ai_b200_attn_fwd_i8_scaled(
+            stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(q_scale), _ptr(kv), _ptr(k_scale), _ptr(v_scale),
+            _ptr(sink_k), _ptr(sink_v), _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
+
     def launch_debug(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, dbg_s, dbg_p, dbg_o):
         batch, seq_len = self._shapes(q, kv, sink_k, sink_v, attn_temperature, out, l)
         cfg = self.config._c()
