@@ -47,3 +47,15 @@ def load_golden(name):
 def code_hist(a, b):
     d = np.abs(a.astype(np.int32) - b.astype(np.int32))
     return np.bincount(d.ravel(), minlength=8)
+
+
+def reference_build_missing(what: str):
+    """oracle/_ref (the reference's own kernels compiled for sm_100a by oracle/build_ref.py) is git-ignored: a
+    fresh clone has none until the recipe has run. Where a checkout of the reference is declared
+    (X17AI_REFERENCE) its absence is a failure, elsewhere a skip."""
+    import os
+    import pytest
+    msg = f"oracle/_ref has no {what} (python oracle/build_ref.py <reference checkout>)"
+    if os.environ.get("X17AI_REFERENCE"):
+        pytest.fail(msg + ": X17AI_REFERENCE is set, so __graft_entry__.build() should have made it")
+    pytest.skip(msg)

@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import load_golden, reference_build_missing
 from oracle import gemm as o_gemm
 
 pytestmark = pytest.mark.gpu
@@ -25,7 +25,7 @@ def _run_reference(stream, fixture, kind, a, b, c_shape, c_dtype, rrms_shape=Non
     from x17ai_b200.kernel_objects import CubinKernel
     d = REF / f"gemm_{kind}_{fixture}"
     if not (d / "kernel.cubin").exists():
-        pytest.skip(f"oracle/_ref has no {kind} kernel for {fixture}")
+        reference_build_missing(f"{kind} kernel for {fixture}")
     meta = json.loads((d / "meta.json").read_text())
     ta, tb = torch.from_numpy(np.ascontiguousarray(a)).cuda(), torch.from_numpy(np.ascontiguousarray(b)).cuda()
     c = torch.zeros(c_shape, dtype=c_dtype, device="cuda")

@@ -18,7 +18,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import code_hist, load_golden
+from conftest import code_hist, load_golden, reference_build_missing
 from oracle import attn as o_attn, formats
 
 pytestmark = pytest.mark.gpu
@@ -28,7 +28,7 @@ REF = Path(__file__).resolve().parent.parent / "oracle" / "_ref"
 def _ref_dir(H, D):
     d = REF / f"attn_h{H}_d{D}"
     if not (d / "kernel.cubin").exists():
-        pytest.skip("oracle/_ref not built (python oracle/build_ref.py <reference checkout>)")
+        reference_build_missing(f"attention kernel for {H} heads x {D}")
     return d
 
 
