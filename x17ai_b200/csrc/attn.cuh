@@ -62,7 +62,7 @@ constexpr u32 ROW_THREADS = ROW_WARPS * 32;
 constexpr u32 THREADS = 64 + ROW_THREADS;
 constexpr u32 TMEM_COLS = 256;
 constexpr u32 O_COL = 128;
-constexpr u32 XCHG_BYTES = ROW_THREADS * 4 + 128 * 4;  // the row pairs' exchange area, then the head's sink values as f32
+constexpr u32 XCHG_BYTES = ROW_THREADS * 4 + 128 * 4 + 128;  // the row pairs' exchange area, the head's sink values as f32, its sink key
 template <u32 D>
 constexpr u32 smem_bytes() {
 	return BQ * D + STAGES * BKV * D + BQ * BKV + XCHG_BYTES + 1024 + 256;
@@ -223,6 +223,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 	constexpr u32 BAR_OFF = XCHG_OFF + XCHG_BYTES;
 	f32 *const xchg = reinterpret_cast<f32 *>(smem_gen + XCHG_OFF);
 	f32 *const svf = xchg + ROW_THREADS;
+	u8 *const sks = reinterpret_cast<u8 *>(svf + 128);   // the head's sink key (D bytes)
 	u32 const bar_base = smem_base + BAR_OFF;
 	auto full_bar = [&](u32 s) { return bar_base + 8 * s; };
 	auto empty_bar = [&](u32 s) { return bar_base + 8 * (STAGES + s); };
@@ -251,6 +252,10 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 	u32 const t_begin = (w == 0xFFFFFFFFu || q0 < w) ? 0u : (q0 - w) / BKV;
 	u32 const t_end = q_tile;  // inclusive; BQ == BKV, so the diagonal tile has the CTA's index
 
+	// ring entries that thread 0 requests itself right after it has initialised the barriers (below)
+	u32 const n_sweep1 = t_end - t_begin + 1;
+	u32 const n_early = n_sweep1 < STAGES ? n_sweep1 : STAGES;
+
 	if (threadIdx.x == 0) {
 		for (u32 s = 0; s < STAGES; ++s) {
 			mbar_init(full_bar(s), 1);
@@ -266,6 +271,18 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		mbar_init(pv_done_bar, 1);
 		*abort_flag = 0;
 		mbar_fence_init();
+		fence_proxy_async_smem();
+		// Q and the first K tiles are requested before the CTA's set-up barrier: nothing has used the ring yet, so
+		// no "empty" wait is needed, and their latency runs under the TMEM allocation
+		tma_prefetch_desc(tm_q_ptr);
+		tma_prefetch_desc(tm_kv_ptr);
+		mbar_expect_tx(q_full_bar, BQ * D);
+		tma_load_3d(s_q, tm_q_ptr, q_full_bar, i32(head * D), i32(q0), i32(batch));
+		for (u32 s = 0; s < n_early; ++s) {
+			mbar_expect_tx(full_bar(s), TILE_BYTES);
+			tma_load_3d(s_ring + s * TILE_BYTES, tm_kv_ptr, full_bar(s), i32(2 * head * D), i32((t_begin + s) * BKV),
+						i32(batch));
+		}
 	}
 	if (warp == 1) {
 		tmem_alloc(tmem_slot, TMEM_COLS);
@@ -278,12 +295,8 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 
 	if (warp == 0) {
 		// ---------------- TMA producer ----------------
-		if (elect_one()) {
-			tma_prefetch_desc(tm_q_ptr);
-			tma_prefetch_desc(tm_kv_ptr);
-			mbar_expect_tx(q_full_bar, BQ * D);
-			tma_load_3d(s_q, tm_q_ptr, q_full_bar, i32(head * D), i32(q0), i32(batch));
-			u32 it = 0;
+		if (lane == 0) {
+			u32 it = n_early;   // thread 0 has already requested Q and the first K tiles of sweep 1
 			bool ok = true;
 			// one ring entry: the K (item 0) or V (item 1) tile of KV tile t
 			auto load = [&](u32 t, u32 item) -> bool {
@@ -299,7 +312,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			// sweep 1: K tiles. sweep 2, in the order the MMA warp consumes them:
 			// K[first], then K[t+1] before V[t] (Q.K^T of the next tile is issued ahead of P.V)
 			#pragma unroll 1
-			for (u32 t = t_begin; t <= t_end && ok; ++t) ok = load(t, 0);
+			for (u32 t = t_begin + n_early; t <= t_end && ok; ++t) ok = load(t, 0);
 			if (ok) ok = load(t_begin, 0);
 			#pragma unroll 1
 			for (u32 t = t_begin; t <= t_end && ok; ++t) {
@@ -406,22 +419,6 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		u32 const xid = half * BQ + row;       // own slot in the exchange area
 		u32 const xpartner = (half ^ 1u) * BQ + row;
 
-		// sink score: exact int32 dot product of this row's q with sink_k
-		i32 sink_dot = 0;
-		if (row_ok) {
-			uint4 const *qrow = reinterpret_cast<uint4 const *>(
-				p.q + u64(batch) * p.q_batch_stride + u64(qi) * p.q_stride + head * D);
-			uint4 const *sk = reinterpret_cast<uint4 const *>(p.sink_k + head * D);
-#pragma unroll
-			for (u32 i = 0; i < D / 16; ++i) {
-				uint4 a = qrow[i];
-				uint4 b = __ldg(sk + i);
-				sink_dot = __dp4a(i32(a.x), i32(b.x), sink_dot);
-				sink_dot = __dp4a(i32(a.y), i32(b.y), sink_dot);
-				sink_dot = __dp4a(i32(a.z), i32(b.z), sink_dot);
-				sink_dot = __dp4a(i32(a.w), i32(b.w), sink_dot);
-			}
-		}
 		// temperature (attn_fwd_i8.cuh:444-450, :497)
 		u32 const n_att = (qi < w ? qi : w) + 4u;
 		f32 const base_t = f32((1.0 / 64.0) * (D == 128 ? 0.08838834764831845 : D == 64 ? 0.125 : 0.17677669529663687));
@@ -434,14 +431,12 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		f32 const a_row = SCALED ? __fmul_rn(__fmul_rn(temp, 64.0f), row_ok ? __ldg(p.tok_q_scale + tok_base + qi) : 0.125f) : 0.0f;
 		f32 const *const ksc = SCALED ? p.tok_k_scale + tok_base : nullptr;
 		f32 const *const vsc = SCALED ? p.tok_v_scale + tok_base : nullptr;
-		// the sink key and value are FixedI8 (scale 1/8) in every mode
-		f32 const sink_s = SCALED ? __fmul_rn(__fmul_rn(__int2float_rn(sink_dot), a_row), 0.125f)
-								  : __fmul_rn(__int2float_rn(sink_dot), temp);
-
-		// the head's sink values as f32, once per CTA (read in the epilogue, two named barriers later)
+		// the head's sink values as f32 and its sink key, once per CTA (the key is read after sweep 1, one
+		// named barrier later; the values in the epilogue)
 		if (threadIdx.x - 64u < D) {
 			u32 const b = reinterpret_cast<u8 const *>(p.sink_v)[head * D + (threadIdx.x - 64u)];
 			svf[threadIdx.x - 64u] = FP8PV ? hw_e4m3_to_f32(b) : f32(i32(i8(b)));
+			sks[threadIdx.x - 64u] = reinterpret_cast<u8 const *>(p.sink_k)[head * D + (threadIdx.x - 64u)];
 		}
 
 		u32 use0 = 0, use1 = 0;  // how often S buffer 0 / 1 has been consumed
@@ -491,21 +486,21 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 					scaled_extreme_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
 					scaled_extreme_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
 				}
-			} else if (edge) {
-				if (pos_t) {
-					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
-					extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
-				} else {
-					extreme_chunk<true, false>(r0, col_base, lo, span, ext);
-					extreme_chunk<true, false>(r1, col_base + 32, lo, span, ext);
-				}
-			} else {
+			} else if (!edge) {
 				if (pos_t) {
 					extreme_chunk<false, true>(r0, col_base, lo, span, ext);
 					extreme_chunk<false, true>(r1, col_base + 32, lo, span, ext);
 				} else {
 					extreme_chunk<false, false>(r0, col_base, lo, span, ext);
 					extreme_chunk<false, false>(r1, col_base + 32, lo, span, ext);
+				}
+			} else {
+				if (pos_t) {
+					extreme_chunk<true, true>(r0, col_base, lo, span, ext);
+					extreme_chunk<true, true>(r1, col_base + 32, lo, span, ext);
+				} else {
+					extreme_chunk<true, false>(r0, col_base, lo, span, ext);
+					extreme_chunk<true, false>(r1, col_base + 32, lo, span, ext);
 				}
 			}
 			if constexpr (DEBUG) {
@@ -529,7 +524,29 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		}
 		if constexpr (SCALED) cand = m_loc;
 		xchg[xid] = cand;
-		named_barrier_sync(1, ROW_THREADS);
+		named_barrier_sync(1, ROW_THREADS);   // also: sks has been written
+		// sink score: exact int32 dot product of this row's q with sink_k (the sink key and value are FixedI8,
+		// scale 1/8, in every mode). q comes from the Q tile in shared memory, after the first sweep: reading the
+		// row from global memory in front of the sweep cost every CTA some four thousand cycles of load latency.
+		i32 sink_dot = 0;
+		if (ok && mbar_wait_warp(q_full_bar, 0, ctx, ST_WAIT_Q_FULL, 1)) {
+			// 16-byte chunks of a Q row are XOR-swizzled by the row index the way the TMA wrote them
+			u32 const q_swz = D == 128 ? (row & 7u) : D == 64 ? ((row >> 1) & 3u) : ((row >> 2) & 1u);
+			u8 const *qrow = smem_gen + row * D;
+#pragma unroll
+			for (u32 i = 0; i < D / 16; ++i) {
+				uint4 const a = *reinterpret_cast<uint4 const *>(qrow + ((i ^ q_swz) << 4));
+				uint4 const b = *reinterpret_cast<uint4 const *>(sks + 16 * i);
+				sink_dot = __dp4a(i32(a.x), i32(b.x), sink_dot);
+				sink_dot = __dp4a(i32(a.y), i32(b.y), sink_dot);
+				sink_dot = __dp4a(i32(a.z), i32(b.z), sink_dot);
+				sink_dot = __dp4a(i32(a.w), i32(b.w), sink_dot);
+			}
+		} else {
+			ok = false;
+		}
+		f32 const sink_s = SCALED ? __fmul_rn(__fmul_rn(__int2float_rn(sink_dot), a_row), 0.125f)
+								  : __fmul_rn(__int2float_rn(sink_dot), temp);
 		f32 const m = fmaxf(sink_s, fmaxf(cand, xchg[xpartner]));
 		named_barrier_sync(1, ROW_THREADS);  // the exchange area is reused for the sums
 		// per-token-scale mode: g = 2^(mz - m), the largest 2^(x - m) * v_scale of the row; P = 255 * (...) / g
@@ -565,12 +582,12 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			if (edge) visible(k0, lo, span);
 			u32 r0[32], r1[32];
 			u32 const ta = tmem_base + lane_addr + col_base;
+			u32 pk0[8], pk1[8];
 			tmem_ld_32x32b_x32(ta, r0);
 			tmem_ld_32x32b_x32(ta + 32, r1);
 			tmem_wait_ld();
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
-			u32 pk0[8], pk1[8];
 			if constexpr (SCALED) {
 				if (edge) {
 					scaled_softmax_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
@@ -579,12 +596,12 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 					scaled_softmax_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
 					scaled_softmax_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
 				}
-			} else if (edge) {
-				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
-				softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
-			} else {
+			} else if (!edge) {
 				softmax_chunk<false, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
 				softmax_chunk<false, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
+			} else {
+				softmax_chunk<true, FP8PV>(r0, col_base, temp, neg_m, lo, span, sum, pk0);
+				softmax_chunk<true, FP8PV>(r1, col_base + 32, temp, neg_m, lo, span, sum, pk1);
 			}
 			if (t > t_begin) {  // P.V of the previous tile has finished reading the P buffer
 				if (!mbar_wait_warp(pv_done_bar, (t - t_begin - 1) & 1, ctx, ST_WAIT_O_FULL, 0x100u + t)) {
@@ -628,17 +645,20 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			u32 const d0 = half * HALF_D;
 			u64 const out_off = u64(batch) * p.o_batch_stride + u64(qi) * p.o_stride + head * D + d0;
 			f32 const vs = FP8PV ? __fmul_rn(recip, __ldg(p.v_scale + head)) : recip;
+			// all of this thread's O columns are requested at once: one load latency per row instead of four
+			u32 r_all[HALF_D / 16][16];
+#pragma unroll
+			for (u32 c = 0; c < HALF_D; c += 16) tmem_ld_32x32b_x16(tmem_base + lane_addr + O_COL + d0 + c, r_all[c / 16]);
+			tmem_wait_ld();
 #pragma unroll
 			for (u32 c = 0; c < HALF_D; c += 16) {
-				u32 r[16];
-				tmem_ld_32x32b_x16(tmem_base + lane_addr + O_COL + d0 + c, r);
+				u32 const (&r)[16] = r_all[c / 16];
 				f32 sv[16];
 #pragma unroll
 				for (u32 i = 0; i < 16; i += 4) {
 					float4 const s4 = *reinterpret_cast<float4 const *>(svf + d0 + c + i);
 					sv[i] = s4.x; sv[i + 1] = s4.y; sv[i + 2] = s4.z; sv[i + 3] = s4.w;
 				}
-				tmem_wait_ld();
 				if constexpr (FP8PV) {
 					// O is f32 = sum of (256 p) * e4m3(v); sink_v is e4m3 too; out = bf16(value * v_scale)
 					u32 o2[8];
