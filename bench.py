@@ -85,18 +85,48 @@ def library_tensor_peaks(torch, dev):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+    """Samples SM clocks, power and throttle reasons during the timed region: through NVML every 5 ms from a
+    thread of this process (read-only queries; a timed region of a few milliseconds still gets samples) and,
+    beside it, with the nvidia-smi query loop every 100 ms. The summary uses the NVML samples when there are
+    any, else nvidia-smi's."""
 
     Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    PERIOD_S = 0.005
 
     def __init__(self, index):
         self.index = index
         self.proc = None
         self.lines = []
+        self.nvml = []        # (wall time, sm MHz, max MHz, watts, reason bits)
+        self._stop = threading.Event()
+        self._nvml_thread = None
+
+    def _nvml_loop(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        except Exception:
+            return
+        while not self._stop.is_set():
+            try:
+                self.nvml.append((time.time(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), mx,
+                                  nv.nvmlDeviceGetPowerUsage(h) / 1000.0, int(reasons(h))))
+            except Exception:
+                pass
+            self._stop.wait(self.PERIOD_S)
+        try:
+            nv.nvmlShutdown()
+        except Exception:
+            pass
 
     def start(self):
+        self._nvml_thread = threading.Thread(target=self._nvml_loop, daemon=True)
+        self._nvml_thread.start()
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -110,19 +140,35 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    # NVML's reason bits (nvml.h: nvmlClocksEventReasons)
+    BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
     def stop(self, t_begin=None, t_end=None):
         """Summary of the samples taken between the wall-clock times t_begin and t_end (all if None)."""
         import datetime
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        self._stop.set()
+        if self._nvml_thread is not None:
+            self._nvml_thread.join(timeout=2)
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        all_bits = 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        power = []
+        for ts, c, m, w, bits in self.nvml:
+            if t_begin is not None and not (t_begin - 0.002 <= ts <= t_end + 0.002):
+                continue
+            sm.append(float(c)); mx.append(float(m)); power.append(w)
+            all_bits |= bits
+            for n, b in self.BITS.items():
+                if bits & b:
+                    reasons.add(n)
+        source = "nvml, 5 ms period"
+        smi = 0
+        smi_rows = []
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 8:
@@ -131,14 +177,24 @@ class ClockSampler:
                 ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
                 if t_begin is not None and not (t_begin - 0.05 <= ts <= t_end + 0.05):
                     continue
-                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
+                smi_rows.append((float(parts[1]), float(parts[2]), float(parts[3]), parts[4:8]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[4:8]):
+        smi = len(smi_rows)
+        if not sm:
+            if self.proc is None and not smi_rows:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml and nvidia-smi unavailable"]}
+            source = "nvidia-smi, 100 ms period"
+            for c, m, w, flags in smi_rows:
+                sm.append(c); mx.append(m); power.append(w)
+        for c, m, w, flags in smi_rows:      # reasons seen by either sampler count
+            for n, v in zip(names, flags):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "sm_mhz_lowest": min(sm) if sm else None, "sm_mhz_highest": max(sm) if sm else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_nvidia_smi": smi,
+                "source": source, "reasons": sorted(reasons), "nvml_reason_bits": hex(all_bits)}
 
 
 def measured_traffic(workload, units):
@@ -959,12 +1015,22 @@ class Runner:
         torch = self.torch
         sync = sync or self.stream.synchronize
         timers = [self.device.CudaTimer(self.stream) for _ in range(steps)]
+        tw = time.perf_counter()
         for _ in range(warmup):
             step()
         sync()
+        per_step = (time.perf_counter() - tw) / max(warmup, 1)
         sampler = ClockSampler(self.local)
         sampler.start()
-        time.sleep(0.5)  # nvidia-smi needs a moment before its first sample
+        # nvidia-smi needs half a second before its first sample. The GPU keeps working through it (more untimed
+        # steps): after an idle half second the first timed steps would run while the clocks are still ramping up.
+        # Every rank runs the same number of them (a step may hold a collective).
+        n_keep = torch.tensor([min(int(PRELOAD_S / max(per_step, 1e-6)) + 1, 200000)], dtype=torch.int64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(n_keep, op=self.dist.ReduceOp.MAX)
+        for _ in range(int(n_keep[0])):
+            step()
+        sync()
         self.barrier()
         launches0 = self.lib.x17ai_b200_launch_count()
         wall0 = time.time()
@@ -1004,16 +1070,27 @@ class Runner:
         return int(min(hi, max(lo, np.ceil(seconds / per))))
 
 
-def roofline(w, achieved, region_s, peaks, lib_peaks, traffic_key):
+PRELOAD_S = 0.5   # the step runs back to back for this long right before the timed region (Runner.time_steps)
+
+
+def roofline(w, achieved, region_s, peaks, lib_peaks, traffic_key, clocks=None):
     """`peak`: the measured denominator of MEASURED_PEAKS.json - for a tensor-bound kernel twice the cuBLAS bf16
-    rate (int8 and fp8 run at twice the bf16 rate; no int8 figure is in that file), the burst figure for a timed
-    region under a second, the sustained one for a longer region; for an HBM-bound kernel the copy bandwidth."""
+    rate (int8 and fp8 run at twice the bf16 rate; no int8 figure is in that file); for an HBM-bound kernel the
+    copy bandwidth. That file has a burst figure (a kernel timed alone) and a sustained one (a seconds-long loop
+    under the power cap). The timed region here follows half a second of the same step, so the sustained figure
+    is the denominator when the load has lasted a second by the end of the region or the clock record shows the
+    power cap active; else the burst one. Both fractions are in the line."""
     if w.bound == "tensor":
-        burst = region_s < 1.0
+        capped = bool(clocks) and "sw_power_cap" in (clocks.get("reasons") or [])
+        burst = (PRELOAD_S + region_s) < 1.0 and not capped
         peak = 2.0 * (peaks["bf16_burst"] if burst else peaks["bf16_sustained"])
+        why = (f"{PRELOAD_S:.1f} s of the same step before a timed region of {region_s:.2f} s"
+               + ("; sw_power_cap active in the clock record" if capped else ""))
         r = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
              "traffic": measured_traffic(traffic_key, w.units),
-             "peak_source": f"2 x bf16 {'burst' if burst else 'sustained'} of {peaks['source']} (timed region {region_s:.2f} s)",
+             "peak_source": f"2 x bf16 {'burst' if burst else 'sustained'} of {peaks['source']} ({why})",
+             "frac_of_burst": achieved / (2.0 * peaks["bf16_burst"]),
+             "frac_of_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
              "nominal_frac": achieved / 4500.0}
         key = "fp8_tflops" if "e4m3" in w.dtype and "s8" not in w.dtype else "int8_tops"
         if lib_peaks.get(key):
@@ -1140,9 +1217,10 @@ def main():
         "dtype": w.dtype, "data": "synthetic (seeded N(0,1) values quantised to FixedI8 codes)",
         "config": dict(w.config, sharding=(
             f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path"
-            if strong else f"{world} x per-GPU workload, token-row units, no collective")),
+            if strong else f"{world} x per-GPU workload, token-row units, no collective"),
+            load_before_timed_region=f"{PRELOAD_S} s of the same step after the warm-up steps, back to back"),
         "tokens_per_s": tokens_job * args.steps / dev_total,
-        "roofline": dict(roofline(w, achieved, dev_total, peaks, lib_peaks, args.workload), kernel_ms=kernel_avg * 1e3),
+        "roofline": dict(roofline(w, achieved, dev_total, peaks, lib_peaks, args.workload, clocks), kernel_ms=kernel_avg * 1e3),
         "clocks": clocks,
         "gpu_launches": int(launches),
         "wall_ms_per_step": wall_total / args.steps * 1e3,
@@ -1187,7 +1265,7 @@ def main():
                 side[name] = {"metric": METRICS[name], "value": work * n / d_total / sc, "unit": u, "steps": n,
                               "ms_per_step": d_total / n * 1e3, "tokens_per_s": sw.tokens * n / d_total, "dtype": sw.dtype,
                               "config": sw.config, "gpu_launches": n_launch, "clocks": clk,
-                              "roofline": roofline(sw, work / k_avg / sc, d_total, peaks, lib_peaks, name)}
+                              "roofline": roofline(sw, work / k_avg / sc, d_total, peaks, lib_peaks, name, clk)}
                 del sw
             except Exception as e:   # one workload must not cost the headline its line
                 side[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
