@@ -319,8 +319,7 @@ x17ai_DiagnosticBuffer *attn_launch(
 struct GemmPlan {
 	int epi;     // x17::GemmEpilogue
 	bool f8;     // kind::f8f6f4
-	bool split;  // e4m3 activations x split int8 weights: two e4m3 planes per weight row
-	int kind() const { return split ? x17::gemm_cfg::KIND_F8_SPLIT : f8 ? x17::gemm_cfg::KIND_F8 : x17::gemm_cfg::KIND_I8; }
+	bool split;  // e4m3 activations x split int8 weights: K doubled, A repeated
 };
 
 x17ai_DiagnosticBuffer *plan_gemm(x17ai_GemmConfig const *cfg, GemmPlan *plan, char const *who) {
@@ -425,31 +424,19 @@ void fill_gemm_params(x17ai_GemmConfig const *cfg, GemmPlan const &plan, size_t 
 	}
 }
 
-template <int EPI, int KIND>
-cudaError_t gemm_go_kind(dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
-						 x17::GemmParams const &p) {
-	uint32_t const smem = x17::gemm_cfg::smem_bytes(KIND);
-	cudaError_t const ce =
-		cudaFuncSetAttribute(x17::gemm_kernel<EPI, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-	if (ce != cudaSuccess) return ce;
-	x17::gemm_kernel<EPI, KIND><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb, p);
-	return cudaSuccess;
-}
-
 template <int EPI>
-cudaError_t gemm_go(int kind, dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
+cudaError_t gemm_go(bool f8, dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
 					x17::GemmParams const &p) {
-	using namespace x17::gemm_cfg;
+	uint32_t const smem = x17::gemm_cfg::SMEM_BYTES;
 	cudaError_t ce;
-	if (kind == KIND_F8_SPLIT) {
-		ce = gemm_go_kind<EPI, KIND_F8_SPLIT>(grid, stream, ta, tb, p);
+	if (f8) {
+		ce = cudaFuncSetAttribute(x17::gemm_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
 		if (ce != cudaSuccess) return ce;
-	} else if (kind == KIND_F8) {
-		ce = gemm_go_kind<EPI, KIND_F8>(grid, stream, ta, tb, p);
-		if (ce != cudaSuccess) return ce;
+		x17::gemm_kernel<EPI, true><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb, p);
 	} else {
-		ce = gemm_go_kind<EPI, KIND_I8>(grid, stream, ta, tb, p);
+		ce = cudaFuncSetAttribute(x17::gemm_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
 		if (ce != cudaSuccess) return ce;
+		x17::gemm_kernel<EPI, false><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb, p);
 	}
 	return cudaSuccess;
 }
@@ -591,7 +578,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stre
 	desc->k2 = p.k2;
 	desc->k3 = p.k3;
 	desc->k4 = p.k4;
-	desc->smem_bytes = smem_bytes(plan.kind());
+	desc->smem_bytes = SMEM_BYTES;
 	desc->threads = THREADS;
 	desc->m_per_block = BM;
 	desc->n_per_block = BN;
@@ -600,10 +587,9 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_object_desc(x17ai_CudaStreamHandle *stre
 	// A's row count are written by the kernel object itself at launch
 	void *const dummy = reinterpret_cast<void *>(uintptr_t(1) << 20);
 	CUtensorMap ta, tb;
-	uint32_t const kbox = k_box(plan.kind());
-	CUresult e = make_map_2d(&ta, dummy, cfg->a_cols, BM, cfg->a_cols, kbox, BM);
+	CUresult e = make_map_2d(&ta, dummy, cfg->a_cols, BM, cfg->a_cols, BK, BM);
 	// B: the int8 weights [N, K], or the object's own two e4m3 planes [N, 2K] of them
-	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, dummy, p.k, cfg->b_rows, p.k, kbox, BN);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, dummy, p.k, cfg->b_rows, p.k, BK, BN);
 	if (e != CUDA_SUCCESS) {
 		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who, ": cuTensorMapEncodeTiled failed: ",
 						 x17::cu_error_text(e));
@@ -1030,7 +1016,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_meta(x17ai_GemmConfig const *cfg, x17ai_
 	if (auto *d = plan_gemm(cfg, &plan, "x17ai_b200_gemm_meta()")) return d;
 	if (meta == nullptr) return static_diag("x17ai_b200_gemm_meta(): null argument");
 	meta->threads_per_block = x17::gemm_cfg::THREADS;
-	meta->smem_bytes = x17::gemm_cfg::smem_bytes(plan.kind());
+	meta->smem_bytes = x17::gemm_cfg::SMEM_BYTES;
 	meta->m_per_block = x17::gemm_cfg::BM;
 	meta->n_per_block = x17::gemm_cfg::BN;
 	return nullptr;
@@ -1068,9 +1054,8 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	size_t const k_a = cfg->a_cols;
 	size_t const k_total = plan.split ? 2 * k_a : k_a;
 	CUtensorMap ta, tb;
-	uint32_t const kbox = k_box(plan.kind());   // K bytes per ring stage = inner extent of both boxes
-	CUresult e = make_map_2d(&ta, a, k_a, a_rows, k_a, kbox, BM);
-	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, b, k_total, cfg->b_rows, k_total, kbox, BN);
+	CUresult e = make_map_2d(&ta, a, k_a, a_rows, k_a, BK, BM);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, b, k_total, cfg->b_rows, k_total, BK, BN);
 	if (e != CUDA_SUCCESS) {
 		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
 						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
@@ -1087,12 +1072,12 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 	cudaError_t ce;
 	switch (plan.epi) {
-	case x17::EPI_SCALE_I8: ce = gemm_go<x17::EPI_SCALE_I8>(plan.kind(), grid, s, ta, tb, p); break;
-	case x17::EPI_RAW_I32: ce = gemm_go<x17::EPI_RAW_I32>(plan.kind(), grid, s, ta, tb, p); break;
-	case x17::EPI_L2NORM_KV: ce = gemm_go<x17::EPI_L2NORM_KV>(plan.kind(), grid, s, ta, tb, p); break;
-	case x17::EPI_GEGLU_E4M3: ce = gemm_go<x17::EPI_GEGLU_E4M3>(plan.kind(), grid, s, ta, tb, p); break;
-	case x17::EPI_RESID_E4M3: ce = gemm_go<x17::EPI_RESID_E4M3>(plan.kind(), grid, s, ta, tb, p); break;
-	default: ce = gemm_go<x17::EPI_RESID_I8>(plan.kind(), grid, s, ta, tb, p); break;
+	case x17::EPI_SCALE_I8: ce = gemm_go<x17::EPI_SCALE_I8>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_RAW_I32: ce = gemm_go<x17::EPI_RAW_I32>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_L2NORM_KV: ce = gemm_go<x17::EPI_L2NORM_KV>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_GEGLU_E4M3: ce = gemm_go<x17::EPI_GEGLU_E4M3>(plan.f8, grid, s, ta, tb, p); break;
+	case x17::EPI_RESID_E4M3: ce = gemm_go<x17::EPI_RESID_E4M3>(plan.f8, grid, s, ta, tb, p); break;
+	default: ce = gemm_go<x17::EPI_RESID_I8>(plan.f8, grid, s, ta, tb, p); break;
 	}
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
@@ -1163,7 +1148,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_qkvg_fwd_i8(
 	p.k4 = float(cfg->inp_scale * cfg->out_scale);
 	uint32_t const n_tiles = p.tiles_m * p.tiles_n;
 	uint32_t const ctas = n_tiles < uint32_t(scope.state().sm_count) ? n_tiles : uint32_t(scope.state().sm_count);
-	cudaError_t ce = gemm_go<x17::EPI_QKVG>(x17::gemm_cfg::KIND_I8, dim3(ctas), reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
+	cudaError_t ce = gemm_go<x17::EPI_QKVG>(false, dim3(ctas), reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
 						 cudaGetErrorString(ce));

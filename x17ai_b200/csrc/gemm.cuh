@@ -7,8 +7,7 @@
 // L2NormMatrixWriter (:861-949), GeGluMatrixWriter (:341-441) and ResidualMatrixWriter (:443-622).
 //
 // Structure (one CTA per SM, 192 threads):
-//   warp 0      TMA producer: A tile 128 x 128 B and B tile 256 x 128 B per stage, 128B swizzle (e4m3 x split int8
-//               weights: 128 x 64 B of A beside 256 x 64 B of each weight plane, 64B swizzle, five stages)
+//   warp 0      TMA producer: A tile 128 x 128 B and B tile 256 x 128 B per stage, 128B swizzle
 //   warp 1      MMA issuer: tcgen05.mma kind::i8 (or kind::f8f6f4), M128 N256 K32, accumulators
 //               in TMEM, two accumulator buffers of 256 columns so the epilogue of tile i
 //               overlaps the main loop of tile i+1
@@ -33,7 +32,7 @@ enum GemmEpilogue : int {
 
 struct GemmParams {
 	u32 m, n_raw, k;
-	u32 k_a;  // K extent of A; k == 2 * k_a when B holds the two e4m3 planes of int8 weights (row = [hi(k_a) | lo(k_a)])
+	u32 k_a;  // K extent of A; k == 2 * k_a when B is the split form of int8 weights (A repeats)
 	u32 tiles_m, tiles_n;
 	void *c;
 	u64 c_stride;  // elements of the output type per row
@@ -64,26 +63,6 @@ constexpr u32 STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr u32 THREADS = 192;
 constexpr u32 SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr u32 ACC_COLS = 256;
-
-// Operand kinds. KIND_F8_SPLIT is e4m3 activations x int8 weights held as two e4m3 planes [N][hi(K) | lo(K)]
-// (w = 16 * hi + lo): a stage holds one 64-byte K block of A beside the same block of both planes, so A is fetched
-// once (with a stage per plane it was fetched twice: 96 KB through L2 per 128 K elements instead of 80 KB), and
-// five 40 KB stages keep as many bytes in flight as four 48 KB ones.
-enum : int { KIND_I8 = 0, KIND_F8 = 1, KIND_F8_SPLIT = 2 };
-template <int KIND>
-struct Ring {
-	static constexpr u32 BK = KIND == KIND_F8_SPLIT ? 64 : gemm_cfg::BK;   // bytes = elements
-	static constexpr u32 STAGES = KIND == KIND_F8_SPLIT ? 5 : gemm_cfg::STAGES;
-	static constexpr u32 PLANES = KIND == KIND_F8_SPLIT ? 2 : 1;
-	static constexpr u32 A_BYTES = BM * BK;
-	static constexpr u32 B_BYTES = BN * BK;                                  // one plane
-	static constexpr u32 STAGE_BYTES = A_BYTES + PLANES * B_BYTES;
-	static constexpr u32 SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-};
-constexpr u32 smem_bytes(int kind) {
-	return kind == KIND_F8_SPLIT ? Ring<KIND_F8_SPLIT>::SMEM_BYTES : SMEM_BYTES;
-}
-constexpr u32 k_box(int kind) { return kind == KIND_F8_SPLIT ? Ring<KIND_F8_SPLIT>::BK : BK; }
 }  // namespace gemm_cfg
 
 // ---- epilogue math ---------------------------------------------------------------------------
@@ -140,15 +119,10 @@ X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx
 // The kernel proper. The tensor maps are reached through pointers: kernel parameters for the library's
 // entry points, maps patched on the device for the kernel objects (kernel_objects/gemm.cu). The loop
 // strides over the tiles by `n_ctas`, this CTA being number `cta` of them, whatever the grid's shape.
-template <int EPI, int KIND>
+template <int EPI, bool F8>
 X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr, GemmParams const &p, u32 cta,
 					   u32 n_ctas) {
 	using namespace gemm_cfg;
-	constexpr bool F8 = KIND != KIND_I8;
-	constexpr bool SPLIT = KIND == KIND_F8_SPLIT;
-	using R = Ring<KIND>;
-	constexpr u32 STAGES = R::STAGES, STAGE_BYTES = R::STAGE_BYTES, A_BYTES = R::A_BYTES, B_BYTES = R::B_BYTES,
-				  BK = R::BK;
 	extern __shared__ u8 smem_raw[];
 	u32 const smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	u8 *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -189,7 +163,7 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 	u32 const tmem_base = *tmem_slot_gen;
 
 	u32 const n_tiles = p.tiles_m * p.tiles_n;
-	u32 const k_blocks = (SPLIT ? p.k_a : p.k) / BK;
+	u32 const k_blocks = p.k / BK;
 
 	if (warp == 0) {
 		// ---------------- TMA producer ----------------
@@ -212,14 +186,8 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 					}
 					mbar_expect_tx(full_bar(s), STAGE_BYTES);
 					u32 const a_dst = smem_base + s * STAGE_BYTES;
-					if constexpr (SPLIT) {
-						tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32(kb * BK), m0);
-						tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
-						tma_load_2d(a_dst + A_BYTES + B_BYTES, tm_b_ptr, full_bar(s), i32(p.k_a + kb * BK), n0);
-					} else {
-						tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32((kb * BK) % p.k_a), m0);
-						tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
-					}
+					tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32((kb * BK) % p.k_a), m0);
+					tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
 				}
 			}
 		}
@@ -249,17 +217,13 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 					}
 					tc_fence_after();
 					u32 const a_addr = smem_base + s * STAGE_BYTES;
-					u64 const adesc = make_smem_desc(a_addr, BK);   // rows of BK bytes, swizzled over BK bytes
-					u64 const bdesc = make_smem_desc(a_addr + A_BYTES, BK);
+					u64 const adesc = make_smem_desc(a_addr, 128);
+					u64 const bdesc = make_smem_desc(a_addr + A_BYTES, 128);
 #pragma unroll
 					for (u32 ks = 0; ks < BK / 32; ++ks) {
 						u32 const accumulate = (kb | ks) != 0 ? 1u : 0u;
-						// advance 32 bytes along K inside the swizzle row: +2 in 16-byte units
-						if constexpr (SPLIT) {
-							// both planes of the weights against the one A block (B_BYTES is a multiple of 1024)
-							mma_f8_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
-							mma_f8_ss(d_tmem, adesc + 2 * ks, bdesc + (B_BYTES >> 4) + 2 * ks, idesc, 1u);
-						} else if constexpr (F8) {
+						// advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+						if constexpr (F8) {
 							mma_f8_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
 						} else {
 							mma_i8_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
@@ -501,11 +465,11 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 	}
 }
 
-template <int EPI, int KIND>
+template <int EPI, bool F8>
 __global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
 			const GemmParams p) {
-	gemm_body<EPI, KIND>(&tm_a, &tm_b, p, blockIdx.x, gridDim.x);
+	gemm_body<EPI, F8>(&tm_a, &tm_b, p, blockIdx.x, gridDim.x);
 }
 
 }  // namespace x17

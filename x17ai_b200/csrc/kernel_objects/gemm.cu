@@ -184,6 +184,6 @@ kernel(void const *a, unsigned long long a_rows, void const *b, unsigned long lo
 #if X17_EPI == 3 || X17_EPI == 4
 	p.residual = residual;
 #endif
-	gemm_body<X17_EPI, (X17_SPLIT != 0 ? gemm_cfg::KIND_F8_SPLIT : gemm_cfg::KIND_I8)>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
+	gemm_body<X17_EPI, X17_SPLIT != 0>(reinterpret_cast<CUtensorMap const *>(slot[0].b),
 							  reinterpret_cast<CUtensorMap const *>(slot[1].b), p, cta, n_ctas);
 }
