@@ -489,6 +489,61 @@ class AttnPvFp8(AttnPrefill):
         self.stream.synchronize()
 
 
+class AttnScaled(AttnPrefill):
+    """The benchmark description's input format on the prefill shape: int8 Q/K/V with one f32 scale per token and
+    head (absmax quantisation of N(0,1) values), bf16 output (x17ai_b200_attn_fwd_i8_scaled)."""
+    name = "attention_per_token_scales_prefill"
+    dtype = "s8 (per-token scales)"
+
+    def __init__(self, stream, device, B=8, H=32, S=8192, D=128, W=1024, seed=0):
+        super().__init__(stream, device, B, H, S, D, W, seed)
+        torch = self.torch
+        g = torch.Generator(device=device).manual_seed(seed + 2)
+
+        def quantise(x):   # [B, S, H, D] -> codes [B, S, H, D] int8, scales [B, H, S] f32
+            scale = x.abs().amax(dim=-1).clamp_min(1e-8) / 127.0
+            codes = torch.clamp(torch.round(x / scale[..., None]), -127, 127).to(torch.int8)
+            return codes, scale.permute(0, 2, 1).contiguous().float()
+
+        qc, self.q_scale = quantise(torch.randn(B, S, H, D, generator=g, device=device))
+        self.q.view(B, S, H, D).copy_(qc)
+        kc, self.k_scale = quantise(torch.randn(B, S, H, D, generator=g, device=device))
+        vc, self.v_scale = quantise(torch.randn(B, S, H, D, generator=g, device=device) * 1.3)
+        kv4 = self.kv.view(B, S, H, 2, D)
+        kv4[:, :, :, 0, :] = kc
+        kv4[:, :, :, 1, :] = vc
+        del qc, kc, vc
+        self.out = torch.empty(B, S, H * D, dtype=torch.bfloat16, device=device)
+        self.alg_bytes = (self.q.numel() + self.kv.numel() + 2 * self.out.numel() + self.l.numel() * 4
+                          + 4 * (self.q_scale.numel() + self.k_scale.numel() + self.v_scale.numel()))
+        self.config = dict(self.config, workload="configs[1] attention with per-token-per-head scaled int8 inputs, bf16 out")
+        torch.cuda.synchronize()
+
+    def step(self):
+        self.kern.launch_scaled(self.stream, self.q, self.q_scale, self.kv, self.k_scale, self.v_scale, self.sink_k,
+                                self.sink_v, self.temp, self.out, self.l, self.W)
+
+    def host_buffers(self):
+        t = self.torch
+        self.h_q = self.q.cpu().pin_memory(); self.h_kv = self.kv.cpu().pin_memory()
+        self.h_scales = [x.cpu().pin_memory() for x in (self.q_scale, self.k_scale, self.v_scale)]
+        self.h_out = t.empty_like(self.out, device="cpu").pin_memory()
+        self.h2d = self.h_q.numel() + self.h_kv.numel() + sum(4 * x.numel() for x in self.h_scales)
+        self.d2h = self.h_out.numel() * 2
+
+    def e2e_step(self):
+        s = self.stream
+        s.upload(self.h_q.data_ptr(), self.q.data_ptr(), 0, self.h_q.numel())
+        s.upload(self.h_kv.data_ptr(), self.kv.data_ptr(), 0, self.h_kv.numel())
+        for h, d in zip(self.h_scales, (self.q_scale, self.k_scale, self.v_scale)):
+            s.upload(h.data_ptr(), d.data_ptr(), 0, 4 * h.numel())
+        self.step()
+        s.download(self.out.data_ptr(), self.h_out.data_ptr(), 0, self.h_out.numel() * 2)
+
+    def e2e_sync(self):
+        self.stream.synchronize()
+
+
 class Ffn:
     """configs[3]: gated FFN on 16384 tokens, d_model 4096, hidden 14336 (reference GeGLU form)."""
     bound = "tensor"
@@ -888,6 +943,7 @@ def _shape(args, n):
 WORKLOADS = {
     "attn": lambda s, d, a=None, **kw: AttnPrefill(s, d, *(_shape(a, 5) or ()), **kw),
     "attn_pv_fp8": lambda s, d, a=None: AttnPvFp8(s, d, *(_shape(a, 5) or ())),
+    "attn_scaled": lambda s, d, a=None: AttnScaled(s, d, *(_shape(a, 5) or ())),
     "ffn_i8": lambda s, d, a=None: Ffn(s, d, False, *(_shape(a, 3) or ())),
     "ffn_f8": lambda s, d, a=None: Ffn(s, d, True, *(_shape(a, 3) or ())),
     "ffn_e4m3": lambda s, d, a=None: FfnE4m3(s, d, *(_shape(a, 3) or ())),
@@ -897,14 +953,16 @@ WORKLOADS = {
     "block": lambda s, d, a=None: Block(s, d, *(_shape(a, 7) or ())),
 }
 METRICS = {"attn": "int8 sliding-window attention prefill throughput",
-           "attn_pv_fp8": "attention with fp8 P.V prefill throughput", "ffn_i8": "gated FFN forward throughput",
+           "attn_pv_fp8": "attention with fp8 P.V prefill throughput",
+           "attn_scaled": "attention with per-token-per-head scaled int8 inputs prefill throughput",
+           "ffn_i8": "gated FFN forward throughput",
            "qkvg": "fused Q/KV projection throughput", "ffn_f8": "gated FFN forward throughput",
            "ffn_e4m3": "gated FFN forward throughput (e4m3 weights and activations)",
            "decode": "int8 decode attention KV-cache bandwidth", "rms_norm": "RMSNorm bandwidth",
            "block": "quantized block forward throughput"}
 # the other kernels of the path, reported beside the headline at N = 1 (smaller than the headline's own case
 # only where the full one would not fit the few minutes the default run has)
-SIDE_WORKLOADS = ["ffn_i8", "ffn_f8", "ffn_e4m3", "qkvg", "attn_pv_fp8", "decode", "rms_norm", "block"]
+SIDE_WORKLOADS = ["ffn_i8", "ffn_f8", "ffn_e4m3", "qkvg", "attn_pv_fp8", "attn_scaled", "decode", "rms_norm", "block"]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -921,11 +979,11 @@ def run_reference(args, rank, world):
     except Exception:
         pass
     # build the workload description without touching a GPU
-    cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "ffn_e4m3": Ffn, "decode": Decode,
+    cls = {"attn": AttnPrefill, "attn_pv_fp8": AttnPrefill, "attn_scaled": AttnPrefill, "ffn_i8": Ffn, "ffn_f8": Ffn, "ffn_e4m3": Ffn, "decode": Decode,
            "rms_norm": RmsNorm, "block": Block, "qkvg": Qkvg}[args.workload]
     w = cls.__new__(cls)
-    if args.workload in ("attn", "attn_pv_fp8"):
-        # the fp8 P.V variant has no CPU form of its own: the int8 restatement (same operation count) stands in
+    if args.workload in ("attn", "attn_pv_fp8", "attn_scaled"):
+        # the fp8 P.V and per-token-scale variants: the int8 restatement (same operation count) stands in
         w.S, w.D, w.W, B, H = 8192, 128, 1024, 8, 32
         cfg = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H, "seq_len": 8192,
                "head_dim": 128, "window": 1024}
@@ -1228,7 +1286,7 @@ def main():
     }
     if gather is not None:
         line["gather"] = gather
-    if args.workload in ("attn", "attn_pv_fp8"):
+    if args.workload in ("attn", "attn_pv_fp8", "attn_scaled"):
         line["reference_count_tops"] = (w.ref_ops if strong else world * w.ref_ops) * args.steps / dev_total / 1e12
     if e2e is not None:
         line["e2e"] = e2e

@@ -197,6 +197,49 @@ X17_DEV void scaled_softmax_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 se
 	}
 }
 
+// The same two helpers for a tile that every row sees whole and whose scale vectors can be read four keys at a
+// time (16-byte aligned: seq_len a multiple of 4): no masks, no bounds checks (the tile lies below the diagonal,
+// so its keys exist), a quarter of the loads; the arithmetic and its order are those of the general helpers.
+X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 a_row, f32 const *ksc, f32 const *vsc, f32 &m_loc,
+									   f32 &z_loc) {
+#pragma unroll
+	for (u32 g = 0; g < 8; ++g) {
+		float4 const k4 = __ldg(reinterpret_cast<float4 const *>(ksc) + g);
+		float4 const v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
+		f32 const kf[4] = {k4.x, k4.y, k4.z, k4.w};
+		f32 const vf[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+		for (u32 e4 = 0; e4 < 4; ++e4) {
+			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[4 * g + e4])), a_row), kf[e4]);
+			m_loc = fmaxf(m_loc, x);
+			z_loc = fmaxf(z_loc, __fadd_rn(x, lg2_approx(vf[e4])));
+		}
+	}
+}
+X17_DEV void scaled_softmax_chunk_full(u32 const (&r)[32], f32 a_row, f32 const *ksc, f32 const *vsc, f32 neg_m, f32 rg,
+									   f32 &sum, u32 (&pk)[8]) {
+	using namespace attn_cfg;
+#pragma unroll
+	for (u32 g = 0; g < 8; ++g) {
+		float4 const k4 = __ldg(reinterpret_cast<float4 const *>(ksc) + g);
+		float4 const v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
+		f32 const kf[4] = {k4.x, k4.y, k4.z, k4.w};
+		f32 const vf[4] = {v4.x, v4.y, v4.z, v4.w};
+		u32 q4[4];
+#pragma unroll
+		for (u32 e4 = 0; e4 < 4; ++e4) {
+			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[4 * g + e4])), a_row), kf[e4]);
+			f32 const e = ex2_approx(__fadd_rn(x, neg_m));
+			sum = __fadd_rn(sum, e);
+			f32 const pq = fminf(__fmul_rn(__fmul_rn(e, vf[e4]), rg), 255.0f);
+			q4[e4] = __float_as_uint(__fadd_rn(pq, MAGIC));   // rint(pq) in the low byte
+		}
+		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
+		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
+		pk[g] = __byte_perm(lo2, hi2, 0x5410);
+	}
+}
+
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
 // accumulation in TMEM) and bf16 output; Q.K^T, masks, maximum and normaliser as in the int8 mode.
 // The tensor maps are reached through pointers: kernel parameters for the library's entry points, maps
@@ -431,6 +474,10 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		f32 const a_row = SCALED ? __fmul_rn(__fmul_rn(temp, 64.0f), row_ok ? __ldg(p.tok_q_scale + tok_base + qi) : 0.125f) : 0.0f;
 		f32 const *const ksc = SCALED ? p.tok_k_scale + tok_base : nullptr;
 		f32 const *const vsc = SCALED ? p.tok_v_scale + tok_base : nullptr;
+		// whole tiles may read the scale vectors four keys at a time when every (batch, head) row of them starts
+		// on a 16-byte boundary
+		bool const scales_by_four = SCALED && (p.seq_len & 3u) == 0
+									&& ((reinterpret_cast<u64>(p.tok_k_scale) | reinterpret_cast<u64>(p.tok_v_scale)) & 15u) == 0;
 		// the head's sink values as f32 and its sink key, once per CTA (the key is read after sweep 1, one
 		// named barrier later; the values in the epilogue)
 		if (threadIdx.x - 64u < D) {
@@ -482,6 +529,9 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				if (edge) {
 					scaled_extreme_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
 					scaled_extreme_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+				} else if (scales_by_four) {
+					scaled_extreme_chunk_full(r0, a_row, ksc + k0 + col_base, vsc + k0 + col_base, m_loc, z_loc);
+					scaled_extreme_chunk_full(r1, a_row, ksc + k0 + col_base + 32, vsc + k0 + col_base + 32, m_loc, z_loc);
 				} else {
 					scaled_extreme_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
 					scaled_extreme_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
@@ -592,6 +642,9 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 				if (edge) {
 					scaled_softmax_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
 					scaled_softmax_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
+				} else if (scales_by_four) {
+					scaled_softmax_chunk_full(r0, a_row, ksc + k0 + col_base, vsc + k0 + col_base, neg_m, rg, sum[0], pk0);
+					scaled_softmax_chunk_full(r1, a_row, ksc + k0 + col_base + 32, vsc + k0 + col_base + 32, neg_m, rg, sum[1], pk1);
 				} else {
 					scaled_softmax_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
 					scaled_softmax_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
