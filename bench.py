@@ -1179,6 +1179,8 @@ def main():
     ap.add_argument("--attn-schedule", default="per_tile", choices=["persistent", "per_tile"],
                     help="attention kernel: one CTA per 128-query tile (default) or the persistent one")
     ap.add_argument("--attn-item-tiles", type=int, default=0, help="persistent attention: query tiles per item (0 = per launch)")
+    ap.add_argument("--gemm-tiling", default="cta_pair", choices=["one_cta", "cta_pair"],
+                    help="GEMMs: clusters of two CTAs on 256 x 256 tiles (default) or one CTA per 128 x 256 tile")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()
@@ -1199,6 +1201,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     stream = device.CudaStream(local)
     K.set_attn_schedule(K.ATTN_PER_TILE if args.attn_schedule == "per_tile" else K.ATTN_PERSISTENT, args.attn_item_tiles)
+    K.set_gemm_tiling(K.GEMM_CTA_PAIR if args.gemm_tiling == "cta_pair" else K.GEMM_ONE_CTA)
     run = Runner(torch, dist, lib, device, stream, local, world, dev)
     strong = args.workload == "attn"
     if strong:
@@ -1282,7 +1285,7 @@ def main():
         "clocks": clocks,
         "gpu_launches": int(launches),
         "wall_ms_per_step": wall_total / args.steps * 1e3,
-        "attn_schedule": args.attn_schedule,
+        "attn_schedule": args.attn_schedule, "gemm_tiling": args.gemm_tiling,
     }
     if gather is not None:
         line["gather"] = gather

@@ -244,6 +244,17 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_scaled(
 enum { X17AI_B200_ATTN_PERSISTENT = 0, X17AI_B200_ATTN_PER_TILE = 1 };
 int x17ai_b200_set_attn_schedule(int schedule, unsigned tiles_per_item);
 
+/* Tiling of x17ai_b200_gemm_fwd and x17ai_b200_qkvg_fwd_i8:
+ *   X17AI_B200_GEMM_CTA_PAIR (default): clusters of two CTAs on two SMs, 256 x 256 tiles
+ *     (tcgen05.mma.cta_group::2): every CTA loads its 128 rows of A and half of the tile's rows of B, a third fewer
+ *     bytes per MMA through L2 and shared memory, six ring stages instead of four. Taken for inputs of more than
+ *     128 rows whose N is a multiple of 256; other shapes run the one-CTA form.
+ *   X17AI_B200_GEMM_ONE_CTA: one CTA per SM, 128 x 256 tiles (tcgen05.mma.cta_group::1), the form the kernel
+ *     objects embed (the reference's launch path has no clusters).
+ * The same bytes out. Process-wide; returns 0, or -1 for an unknown value. */
+enum { X17AI_B200_GEMM_ONE_CTA = 0, X17AI_B200_GEMM_CTA_PAIR = 1 };
+int x17ai_b200_set_gemm_tiling(int tiling);
+
 /* Same launch with validation outputs: dbg_s int32 [batch*n_heads][seq][seq] raw scores of the
  * visited tiles, dbg_p uint8 [batch*n_heads][seq][seq] quantised probabilities, dbg_o int32
  * [batch*n_heads][seq][D] the int32 P.V accumulator.  Small shapes only. */

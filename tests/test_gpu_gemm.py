@@ -10,6 +10,16 @@ from oracle import formats, gemm as o_gemm
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["one_cta", "cta_pair"])
+def gemm_tiling(request):
+    """Every test runs with both tilings of the GEMM: one CTA per 128 x 256 tile, and clusters of two CTAs on
+    256 x 256 tiles (taken for inputs of more than 128 rows whose N is a multiple of 256)."""
+    from x17ai_b200 import kernels as K
+    K.set_gemm_tiling(K.GEMM_CTA_PAIR if request.param == "cta_pair" else K.GEMM_ONE_CTA)
+    yield request.param
+    K.set_gemm_tiling()
+
+
 def _rand_i8(rng, shape, std=1.0):
     return formats.quantize_fixedi8(rng.standard_normal(shape) * std)
 

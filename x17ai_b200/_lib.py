@@ -134,6 +134,7 @@ SIGNATURES = {
     "x17ai_b200_gemm_object_desc": (DIAG, [c_void_p, POINTER(GemmConfig), POINTER(GemmObjectDesc)]),
     "x17ai_b200_launch_count": (c_uint64, []),
     "x17ai_b200_set_attn_schedule": (c_int, [c_int, c_uint32]),
+    "x17ai_b200_set_gemm_tiling": (c_int, [c_int]),
 }
 
 _lib = None

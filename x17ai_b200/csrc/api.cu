@@ -28,6 +28,7 @@ namespace {
 
 std::atomic<uint64_t> g_launches{0};
 std::atomic<int> g_attn_schedule{X17AI_B200_ATTN_PER_TILE};
+std::atomic<int> g_gemm_tiling{X17AI_B200_GEMM_CTA_PAIR};
 std::atomic<unsigned> g_attn_item_tiles{0};   // 0 = chosen per launch
 std::mutex g_capture_mutex;
 std::unordered_map<void *, CUcontext> g_capture_ctx;   // streams between graph_begin and graph_end
@@ -424,6 +425,28 @@ void fill_gemm_params(x17ai_GemmConfig const *cfg, GemmPlan const &plan, size_t 
 	}
 }
 
+// The CTA-pair form (gemm.cuh): clusters of two CTAs, one 256 x 256 tile per cluster. `tb_half` is B's map with a box
+// of half a tile's rows. Used for more than one row tile when the tiling is X17AI_B200_GEMM_CTA_PAIR.
+template <int EPI>
+cudaError_t gemm_go_pair(bool f8, int sm_count, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb_half,
+						 x17::GemmParams const &p) {
+	uint32_t const smem = x17::gemm_cfg::PAIR_SMEM_BYTES;
+	uint32_t const tiles = ((p.m + 2 * x17::gemm_cfg::BM - 1) / (2 * x17::gemm_cfg::BM)) * p.tiles_n;
+	uint32_t const clusters = tiles < uint32_t(sm_count / 2) ? tiles : uint32_t(sm_count / 2);
+	dim3 const grid(2 * clusters);
+	cudaError_t ce;
+	if (f8) {
+		ce = cudaFuncSetAttribute(x17::gemm_pair_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+		if (ce != cudaSuccess) return ce;
+		x17::gemm_pair_kernel<EPI, true><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb_half, p);
+	} else {
+		ce = cudaFuncSetAttribute(x17::gemm_pair_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+		if (ce != cudaSuccess) return ce;
+		x17::gemm_pair_kernel<EPI, false><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb_half, p);
+	}
+	return cudaSuccess;
+}
+
 template <int EPI>
 cudaError_t gemm_go(bool f8, dim3 grid, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb,
 					x17::GemmParams const &p) {
@@ -751,6 +774,12 @@ int x17ai_b200_set_attn_schedule(int schedule, unsigned tiles_per_item) {
 	return 0;
 }
 
+int x17ai_b200_set_gemm_tiling(int tiling) {
+	if (tiling != X17AI_B200_GEMM_ONE_CTA && tiling != X17AI_B200_GEMM_CTA_PAIR) return -1;
+	g_gemm_tiling.store(tiling, std::memory_order_relaxed);
+	return 0;
+}
+
 x17ai_DiagnosticBuffer *x17ai_b200_attn_meta(x17ai_AttnConfig const *cfg, x17ai_AttnMeta *meta) {
 	char const *who = "x17ai_b200_attn_meta()";
 	if (auto *d = check_attn_config(cfg, who)) return d;
@@ -1054,8 +1083,10 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	size_t const k_a = cfg->a_cols;
 	size_t const k_total = plan.split ? 2 * k_a : k_a;
 	CUtensorMap ta, tb;
+	bool const pair = g_gemm_tiling.load(std::memory_order_relaxed) == X17AI_B200_GEMM_CTA_PAIR && a_rows > BM
+					  && cfg->b_rows % BN == 0 && scope.state().sm_count >= 2;
 	CUresult e = make_map_2d(&ta, a, k_a, a_rows, k_a, BK, BM);
-	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, b, k_total, cfg->b_rows, k_total, BK, BN);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, b, k_total, cfg->b_rows, k_total, BK, pair ? BN / 2 : BN);
 	if (e != CUDA_SUCCESS) {
 		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
 						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
@@ -1071,6 +1102,17 @@ x17ai_DiagnosticBuffer *x17ai_b200_gemm_fwd(
 	dim3 grid(ctas);
 	cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 	cudaError_t ce;
+	if (pair) {
+		int const sms = scope.state().sm_count;
+		switch (plan.epi) {
+		case x17::EPI_SCALE_I8: ce = gemm_go_pair<x17::EPI_SCALE_I8>(plan.f8, sms, s, ta, tb, p); break;
+		case x17::EPI_RAW_I32: ce = gemm_go_pair<x17::EPI_RAW_I32>(plan.f8, sms, s, ta, tb, p); break;
+		case x17::EPI_L2NORM_KV: ce = gemm_go_pair<x17::EPI_L2NORM_KV>(plan.f8, sms, s, ta, tb, p); break;
+		case x17::EPI_GEGLU_E4M3: ce = gemm_go_pair<x17::EPI_GEGLU_E4M3>(plan.f8, sms, s, ta, tb, p); break;
+		case x17::EPI_RESID_E4M3: ce = gemm_go_pair<x17::EPI_RESID_E4M3>(plan.f8, sms, s, ta, tb, p); break;
+		default: ce = gemm_go_pair<x17::EPI_RESID_I8>(plan.f8, sms, s, ta, tb, p); break;
+		}
+	} else
 	switch (plan.epi) {
 	case x17::EPI_SCALE_I8: ce = gemm_go<x17::EPI_SCALE_I8>(plan.f8, grid, s, ta, tb, p); break;
 	case x17::EPI_RAW_I32: ce = gemm_go<x17::EPI_RAW_I32>(plan.f8, grid, s, ta, tb, p); break;
@@ -1117,8 +1159,10 @@ x17ai_DiagnosticBuffer *x17ai_b200_qkvg_fwd_i8(
 	using namespace x17::gemm_cfg;
 	size_t const n_raw = n_q + n_kv + n_g;
 	CUtensorMap ta, tb;
+	bool const pair = g_gemm_tiling.load(std::memory_order_relaxed) == X17AI_B200_GEMM_CTA_PAIR && rows > BM
+					  && n_raw % BN == 0 && scope.state().sm_count >= 2;
 	CUresult e = make_map_2d(&ta, x, cfg->model_dim, rows, cfg->model_dim, BK, BM);
-	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, w_qkvg, cfg->model_dim, n_raw, cfg->model_dim, BK, BN);
+	if (e == CUDA_SUCCESS) e = make_map_2d(&tb, w_qkvg, cfg->model_dim, n_raw, cfg->model_dim, BK, pair ? BN / 2 : BN);
 	if (e != CUDA_SUCCESS) {
 		return make_diag("x17ai_b200: cuTensorMapEncodeTiled failed", who,
 						 ": cuTensorMapEncodeTiled failed: ", x17::cu_error_text(e));
@@ -1148,7 +1192,9 @@ x17ai_DiagnosticBuffer *x17ai_b200_qkvg_fwd_i8(
 	p.k4 = float(cfg->inp_scale * cfg->out_scale);
 	uint32_t const n_tiles = p.tiles_m * p.tiles_n;
 	uint32_t const ctas = n_tiles < uint32_t(scope.state().sm_count) ? n_tiles : uint32_t(scope.state().sm_count);
-	cudaError_t ce = gemm_go<x17::EPI_QKVG>(false, dim3(ctas), reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
+	cudaError_t const ce =
+		pair ? gemm_go_pair<x17::EPI_QKVG>(false, scope.state().sm_count, reinterpret_cast<cudaStream_t>(stream), ta, tb, p)
+			 : gemm_go<x17::EPI_QKVG>(false, dim3(ctas), reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
 	if (ce != cudaSuccess) {
 		return make_diag("x17ai_b200: cudaFuncSetAttribute failed", who, ": cudaFuncSetAttribute failed: ",
 						 cudaGetErrorString(ce));

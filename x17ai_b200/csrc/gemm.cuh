@@ -63,6 +63,14 @@ constexpr u32 STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr u32 THREADS = 192;
 constexpr u32 SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr u32 ACC_COLS = 256;
+
+// The CTA-pair form: a cluster of two CTAs on two SMs works on one 256 x 256 tile with tcgen05.mma.cta_group::2.
+// Each CTA loads its 128 rows of A and its 128 of the tile's 256 rows of B, so a K block costs a CTA 32 KB instead
+// of 48 KB (59 instead of 89 bytes per MMA cycle and SM) and six stages fit where four did.
+constexpr u32 PAIR_STAGES = 6;
+constexpr u32 PAIR_B_BYTES = (BN / 2) * BK;
+constexpr u32 PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr u32 PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }  // namespace gemm_cfg
 
 // ---- epilogue math ---------------------------------------------------------------------------
@@ -105,8 +113,8 @@ X17_DEV f32 acc_to_f32(u32 bits) {
 // the 148 CTAs then cover a near-square patch of C (16 row tiles x ~9 column tiles) instead of
 // every row tile of one column tile, so a wave touches far fewer distinct rows of A and B and
 // they stay in L2 while the wave needs them.
+template <u32 GROUP_M = 16>
 X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx) {
-	constexpr u32 GROUP_M = 16;
 	u32 const per_group = GROUP_M * tiles_n;
 	u32 const g = t / per_group;
 	u32 const first_m = g * GROUP_M;
@@ -119,10 +127,16 @@ X17_DEV void tile_origin(u32 t, u32 tiles_m, u32 tiles_n, u32 &m_idx, u32 &n_idx
 // The kernel proper. The tensor maps are reached through pointers: kernel parameters for the library's
 // entry points, maps patched on the device for the kernel objects (kernel_objects/gemm.cu). The loop
 // strides over the tiles by `n_ctas`, this CTA being number `cta` of them, whatever the grid's shape.
-template <int EPI, bool F8>
+// PAIR: `cta` / `n_ctas` count clusters of two CTAs, a tile is 256 x 256, and this CTA (rank 0 or 1 of its cluster)
+// owns rows [128 * rank, +128) of it. Rank 0 issues the MMAs for both; both load, both run the epilogue of their rows.
+template <int EPI, bool F8, bool PAIR = false>
 X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr, GemmParams const &p, u32 cta,
 					   u32 n_ctas) {
 	using namespace gemm_cfg;
+	constexpr u32 STAGES = PAIR ? PAIR_STAGES : gemm_cfg::STAGES;
+	constexpr u32 STAGE_BYTES = PAIR ? PAIR_STAGE_BYTES : gemm_cfg::STAGE_BYTES;
+	constexpr u32 TILE_M = PAIR ? 2 * BM : BM;
+	u32 const rank = PAIR ? cluster_cta_rank() : 0u;   // 0: the CTA that issues the MMAs
 	extern __shared__ u8 smem_raw[];
 	u32 const smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	u8 *const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -148,21 +162,28 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 		}
 		for (u32 b = 0; b < 2; ++b) {
 			mbar_init(acc_full_bar(b), 1);
-			mbar_init(acc_empty_bar(b), 4);  // one arrive per epilogue warp
+			mbar_init(acc_empty_bar(b), PAIR ? 8 : 4);  // one arrive per epilogue warp (of both CTAs: rank 0 collects)
 		}
 		*abort_flag = 0;
 		mbar_fence_init();
 	}
 	if (warp == 1) {
-		tmem_alloc(tmem_slot, 512);
-		tmem_relinquish();
+		if constexpr (PAIR) {
+			tmem_alloc_pair(tmem_slot, 512);
+			tmem_relinquish_pair();
+		} else {
+			tmem_alloc(tmem_slot, 512);
+			tmem_relinquish();
+		}
 	}
 	tc_fence_before();
 	__syncthreads();
+	if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
 	tc_fence_after();
 	u32 const tmem_base = *tmem_slot_gen;
 
-	u32 const n_tiles = p.tiles_m * p.tiles_n;
+	u32 const tiles_m = PAIR ? (p.m + TILE_M - 1) / TILE_M : p.tiles_m;
+	u32 const n_tiles = tiles_m * p.tiles_n;
 	u32 const k_blocks = p.k / BK;
 
 	if (warp == 0) {
@@ -174,9 +195,9 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 			bool ok = true;
 			for (u32 t = cta; t < n_tiles && ok; t += n_ctas) {
 				u32 tm, tn;
-				tile_origin(t, p.tiles_m, p.tiles_n, tm, tn);
-				i32 const m0 = i32(tm * BM);
-				i32 const n0 = i32(tn * BN);
+				tile_origin<PAIR ? 8 : 16>(t, tiles_m, p.tiles_n, tm, tn);
+				i32 const m0 = i32(tm * TILE_M + rank * BM);
+				i32 const n0 = i32(tn * BN + (PAIR ? rank * (BN / 2) : 0u));
 				for (u32 kb = 0; kb < k_blocks; ++kb, ++it) {
 					u32 const s = it % STAGES;
 					u32 const ph = (it / STAGES) & 1;
@@ -184,18 +205,35 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 						ok = false;
 						break;
 					}
-					mbar_expect_tx(full_bar(s), STAGE_BYTES);
 					u32 const a_dst = smem_base + s * STAGE_BYTES;
-					tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32((kb * BK) % p.k_a), m0);
-					tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
+					if constexpr (PAIR) {
+						// both CTAs' bytes are counted on rank 0's barrier, where the MMA issuer waits
+						u32 const bar0 = map_to_cta(full_bar(s), 0);
+						if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+						tma_load_2d_pair(a_dst, tm_a_ptr, bar0, i32((kb * BK) % p.k_a), m0);
+						tma_load_2d_pair(a_dst + A_BYTES, tm_b_ptr, bar0, i32(kb * BK), n0);
+					} else {
+						mbar_expect_tx(full_bar(s), STAGE_BYTES);
+						tma_load_2d(a_dst, tm_a_ptr, full_bar(s), i32((kb * BK) % p.k_a), m0);
+						tma_load_2d(a_dst + A_BYTES, tm_b_ptr, full_bar(s), i32(kb * BK), n0);
+					}
 				}
 			}
 		}
 	} else if (warp == 1) {
 		// ---------------- MMA issuer ----------------
-		if (elect_one()) {
-			constexpr u32 idesc = F8 ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 0, BM, BN)
-									 : make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, BM, BN);
+		if (rank == 0 && elect_one()) {
+			constexpr u32 idesc = F8 ? make_idesc(DFMT_F32, FMT_E4M3, FMT_E4M3, 0, 0, TILE_M, BN)
+									 : make_idesc(DFMT_S32, FMT_S8, FMT_S8, 0, 0, TILE_M, BN);
+			// a commit of the pair form arrives on one barrier: this CTA's and, separately, the peer's copy of it
+			auto commit = [&](u32 bar) {
+				if constexpr (PAIR) {
+					tc_commit_pair(map_to_cta(bar, 0));
+					tc_commit_pair(map_to_cta(bar, 1));
+				} else {
+					tc_commit(bar);
+				}
+			};
 			u32 it = 0;
 			u32 local_tile = 0;
 			bool ok = true;
@@ -223,15 +261,18 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 					for (u32 ks = 0; ks < BK / 32; ++ks) {
 						u32 const accumulate = (kb | ks) != 0 ? 1u : 0u;
 						// advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-						if constexpr (F8) {
+						if constexpr (PAIR) {
+							if constexpr (F8) mma_f8_ss_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
+							else mma_i8_ss_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
+						} else if constexpr (F8) {
 							mma_f8_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
 						} else {
 							mma_i8_ss(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, accumulate);
 						}
 					}
-					tc_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+					commit(empty_bar(s));  // frees the stage (in both CTAs) once these MMAs have read it
 				}
-				if (ok) tc_commit(acc_full_bar(buf));
+				if (ok) commit(acc_full_bar(buf));
 			}
 		}
 	} else {
@@ -244,8 +285,8 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 			u32 const buf = local_tile & 1;
 			u32 const acc_ph = (local_tile >> 1) & 1;
 			u32 tm, tn;
-			tile_origin(t, p.tiles_m, p.tiles_n, tm, tn);
-			u32 const m0 = tm * BM;
+			tile_origin<PAIR ? 8 : 16>(t, tiles_m, p.tiles_n, tm, tn);
+			u32 const m0 = tm * TILE_M + rank * BM;
 			u32 const n0 = tn * BN;
 			if (!mbar_wait_warp(acc_full_bar(buf), acc_ph, ctx, ST_WAIT_ACC_FULL, buf)) {
 				ok = false;
@@ -451,17 +492,22 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 			// this warp is done reading the accumulator buffer
 			tc_fence_before();
 			__syncwarp();
-			if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+			if (lane == 0) {
+				if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));
+				else mbar_arrive(acc_empty_bar(buf));
+			}
 		}
 	}
 
 	// teardown: every role falls through to here, also after a wait that gave up
 	tc_fence_before();
 	__syncthreads();
+	if constexpr (PAIR) cluster_sync_all();   // the peer no longer reads this CTA's tiles nor signals its barriers
 	if (warp == 1) {
 		__syncwarp();
 		tc_fence_after();
-		tmem_dealloc(tmem_base, 512);
+		if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 512);
+		else tmem_dealloc(tmem_base, 512);
 	}
 }
 
@@ -470,6 +516,15 @@ __global__ void __launch_bounds__(gemm_cfg::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
 			const GemmParams p) {
 	gemm_body<EPI, F8>(&tm_a, &tm_b, p, blockIdx.x, gridDim.x);
+}
+
+// The CTA-pair form: launched with an even grid; consecutive CTAs form a cluster. The B tensor map's box is the
+// half tile (BN / 2 rows).
+template <int EPI, bool F8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm_cfg::THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+				 const GemmParams p) {
+	gemm_body<EPI, F8, true>(&tm_a, &tm_b, p, blockIdx.x / 2, gridDim.x / 2);
 }
 
 }  // namespace x17

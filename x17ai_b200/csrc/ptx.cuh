@@ -271,6 +271,72 @@ X17_DEV void tc_commit(u32 bar) {
 	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
 				 : "memory");
 }
+// ---- the same for a pair of CTAs on two SMs (a cluster of two): one MMA spans both, each CTA holding its
+// 128 rows of A, its half of B's rows and its 128 lanes of the accumulator. Allocation, release and free are
+// issued by the same warp of both CTAs with the same shared-memory slot offset.
+X17_DEV void tmem_alloc_pair(u32 smem_dst, u32 ncols) {
+	asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+				 : "memory");
+}
+X17_DEV void tmem_relinquish_pair() {
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+X17_DEV void tmem_dealloc_pair(u32 taddr, u32 ncols) {
+	asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrives on `bar` (a shared::cluster address: the issuing CTA's barrier or its peer's) once the pair's MMAs
+// issued so far have completed
+X17_DEV void tc_commit_pair(u32 bar_cluster) {
+	asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+				 : "memory");
+}
+X17_DEV void mma_i8_ss_pair(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 accumulate) {
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+		:
+		: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+X17_DEV void mma_f8_ss_pair(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 accumulate) {
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+		:
+		: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+// TMA tile into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair
+// (`bar_cluster`: a shared::cluster address). Every CTA fetches its own tiles; nothing is multicast.
+X17_DEV void tma_load_2d_pair(u32 dst, CUtensorMap const *map, u32 bar_cluster, i32 x, i32 y) {
+	asm volatile(
+		"cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+		" [%0], [%1, {%3, %4}], [%2];"
+		:
+		: "r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+		: "memory");
+}
+// cluster plumbing
+X17_DEV u32 cluster_cta_rank() {
+	u32 r;
+	asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+	return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+X17_DEV u32 map_to_cta(u32 smem_addr, u32 rank) {
+	u32 r;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+	return r;
+}
+X17_DEV void mbar_arrive_cluster(u32 bar_cluster) {
+	asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+X17_DEV void cluster_sync_all() {
+	asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 X17_DEV void tmem_wait_ld() {
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

@@ -73,6 +73,16 @@ def _dtype_and_device(op, name, t, dtype):
 ATTN_PERSISTENT, ATTN_PER_TILE = 0, 1
 
 
+GEMM_ONE_CTA, GEMM_CTA_PAIR = 0, 1
+
+
+def set_gemm_tiling(tiling: int = GEMM_CTA_PAIR) -> None:
+    """Process-wide tiling of GemmKernel.launch and qkvg_fwd (x17ai_b200_set_gemm_tiling): clusters of two CTAs with
+    256 x 256 tiles (tcgen05.mma.cta_group::2, the default), or one CTA per SM with 128 x 256 tiles. Same bytes out."""
+    if _lib.load().x17ai_b200_set_gemm_tiling(int(tiling)) != 0:
+        raise X17Error(f"unknown GEMM tiling {tiling}")
+
+
 def set_attn_schedule(schedule: int = ATTN_PER_TILE, tiles_per_item: int = 0) -> None:
     """Process-wide choice of the attention kernel (x17ai_b200_set_attn_schedule): the one-CTA-per-query-tile
     kernel (default, the one the kernel objects embed) or the persistent kernel (`tiles_per_item`
