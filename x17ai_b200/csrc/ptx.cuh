@@ -309,7 +309,7 @@ X17_DEV void mma_f8_ss_pair(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 acc
 		: "memory");
 }
 // TMA tile into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair
-// (`bar_cluster`: a shared::cluster address). Every CTA fetches its own tiles; nothing is multicast.
+// (`bar_cluster`: a shared::cluster address). Every CTA fetches its own tiles itself.
 X17_DEV void tma_load_2d_pair(u32 dst, CUtensorMap const *map, u32 bar_cluster, i32 x, i32 y) {
 	asm volatile(
 		"cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
