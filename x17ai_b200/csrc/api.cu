@@ -427,24 +427,59 @@ void fill_gemm_params(x17ai_GemmConfig const *cfg, GemmPlan const &plan, size_t 
 
 // The CTA-pair form (gemm.cuh): clusters of two CTAs, one 256 x 256 tile per cluster. `tb_half` is B's map with a box
 // of half a tile's rows. Used for more than one row tile when the tiling is X17AI_B200_GEMM_CTA_PAIR.
+// How many clusters of the pair kernel the device runs at once. The kernel is persistent, so the grid must not be
+// larger: a cluster needs two free SMs of one GPC, and a GPU whose GPCs have an odd number of usable SMs holds fewer
+// pairs than sm_count / 2; a cluster left over would run alone after all the others. Asked once per kernel and
+// device (the answer depends on neither the stream nor the problem).
+template <typename Kernel>
+uint32_t max_pair_clusters(Kernel kernel, uint32_t smem, int sm_count) {
+	static std::atomic<int> cached[MAX_DEVICES];   // 0 = not asked yet
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return uint32_t(sm_count / 2);
+	int n = cached[dev].load(std::memory_order_relaxed);
+	if (n == 0) {
+		cudaLaunchConfig_t cfg{};
+		cfg.gridDim = dim3(unsigned(sm_count / 2) * 2);
+		cfg.blockDim = dim3(x17::gemm_cfg::THREADS);
+		cfg.dynamicSmemBytes = smem;
+		cudaLaunchAttribute attr{};
+		attr.id = cudaLaunchAttributeClusterDimension;
+		attr.val.clusterDim.x = 2;
+		attr.val.clusterDim.y = 1;
+		attr.val.clusterDim.z = 1;
+		cfg.attrs = &attr;
+		cfg.numAttrs = 1;
+		int active = 0;
+		if (cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) != cudaSuccess || active <= 0) {
+			(void)cudaGetLastError();
+			active = sm_count / 2;
+		}
+		n = active < sm_count / 2 ? active : sm_count / 2;
+		cached[dev].store(n, std::memory_order_relaxed);
+	}
+	return uint32_t(n);
+}
+
+// The CTA-pair form (gemm.cuh): clusters of two CTAs, one 256 x 256 tile per cluster. `tb_half` is B's map with a box
+// of half a tile's rows. Used for more than one row tile when the tiling is X17AI_B200_GEMM_CTA_PAIR.
+template <int EPI, bool F8>
+cudaError_t gemm_go_pair_kind(int sm_count, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb_half,
+							  x17::GemmParams const &p) {
+	uint32_t const smem = x17::gemm_cfg::PAIR_SMEM_BYTES;
+	auto const kernel = x17::gemm_pair_kernel<EPI, F8>;
+	cudaError_t const ce = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+	if (ce != cudaSuccess) return ce;
+	uint32_t const tiles = ((p.m + 2 * x17::gemm_cfg::BM - 1) / (2 * x17::gemm_cfg::BM)) * p.tiles_n;
+	uint32_t const fit = max_pair_clusters(kernel, smem, sm_count);
+	uint32_t const clusters = tiles < fit ? tiles : fit;
+	kernel<<<dim3(2 * clusters), x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb_half, p);
+	return cudaSuccess;
+}
 template <int EPI>
 cudaError_t gemm_go_pair(bool f8, int sm_count, cudaStream_t stream, CUtensorMap const &ta, CUtensorMap const &tb_half,
 						 x17::GemmParams const &p) {
-	uint32_t const smem = x17::gemm_cfg::PAIR_SMEM_BYTES;
-	uint32_t const tiles = ((p.m + 2 * x17::gemm_cfg::BM - 1) / (2 * x17::gemm_cfg::BM)) * p.tiles_n;
-	uint32_t const clusters = tiles < uint32_t(sm_count / 2) ? tiles : uint32_t(sm_count / 2);
-	dim3 const grid(2 * clusters);
-	cudaError_t ce;
-	if (f8) {
-		ce = cudaFuncSetAttribute(x17::gemm_pair_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-		if (ce != cudaSuccess) return ce;
-		x17::gemm_pair_kernel<EPI, true><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb_half, p);
-	} else {
-		ce = cudaFuncSetAttribute(x17::gemm_pair_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-		if (ce != cudaSuccess) return ce;
-		x17::gemm_pair_kernel<EPI, false><<<grid, x17::gemm_cfg::THREADS, smem, stream>>>(ta, tb_half, p);
-	}
-	return cudaSuccess;
+	return f8 ? gemm_go_pair_kind<EPI, true>(sm_count, stream, ta, tb_half, p)
+			  : gemm_go_pair_kind<EPI, false>(sm_count, stream, ta, tb_half, p);
 }
 
 template <int EPI>
