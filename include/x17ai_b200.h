@@ -215,7 +215,7 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
  * x17ai_b200_attn_fwd_i8, which this call equals for q_scale = k_scale = v_scale = 1/8 up to the output format
  * (out = code / 8).  Q.K^T and P.V stay exact integer products on the int8 tensor path:
  *   x[i][j] = (q_i . k_j)_int32 * q_scale[i] * k_scale[j] * D^-1/2 * log2(min(W', i) + 4) * temp_h
- *   P[i][j] = rint(255 * 2^(x - m_i) * v_scale[j] / g_i),  g_i = max_j 2^(x - m_i) * v_scale[j]   (u8)
+ *   P[i][j] = rint(255 * 2^(x - m_i) * v_scale[j] / g_i),  g_i = the largest v_scale[j] among the keys row i sees  (u8)
  *   out[i]  = bf16((g_i / 255 * sum_j P[i][j] v_j + 2^(sink - m_i) * sink_v / 8) / sum_i),  sum_i as before
  *   q_scale, k_scale, v_scale: f32 [batch][n_heads][seq_len];  sink_k, sink_v FixedI8 as before;
  *   out bf16 [batch][seq_len][o_stride] (o_stride in elements);  l [batch][n_heads][seq_len] or NULL.

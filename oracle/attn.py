@@ -251,8 +251,9 @@ def attn_fwd_i8_scaled(q, q_scale, k, k_scale, v, v_scale, sink_k, sink_v, tempe
     pinned by this restatement only, and by its case q_scale = k_scale = v_scale = 1/8, which is attn_head.
       q, k, v int8 [S, H, D]; q_scale, k_scale, v_scale f32 [H, S]; sink_k, sink_v int8 [H, D] (FixedI8, code / 8);
       returns out f64 [S, H, D] (before the bf16 cast) and l f32 [H, S].
-    `quantise_p` models the kernel's u8 probabilities P = rint(255 * 2^(x - m) * v_scale / g), g the row's largest
-    2^(x - m) * v_scale; without it the result is the plain float64 softmax attention of the dequantised inputs."""
+    `quantise_p` models the kernel's u8 probabilities P = rint(255 * 2^(x - m) * v_scale / g), g the largest v_scale
+    among the row's visible keys (so P <= 255 without a second maximum over the scores); without it the result is the
+    plain float64 softmax attention of the dequantised inputs."""
     q = np.asarray(q, dtype=np.int8); k = np.asarray(k, dtype=np.int8); v = np.asarray(v, dtype=np.int8)
     s_len, n_heads, d = q.shape
     w = _round_window(window)
@@ -277,7 +278,7 @@ def attn_fwd_i8_scaled(q, q_scale, k, k_scale, v, v_scale, sink_k, sink_v, tempe
         vs = v_scale[h].astype(np.float64)
         if quantise_p:
             wgt = e * vs[None, :]
-            g = wgt.max(axis=1)
+            g = np.where(mask, 0.0, vs[None, :]).max(axis=1)       # the largest v_scale among the row's visible keys
             p8 = np.where(g[:, None] > 0, np.rint(255.0 * wgt / np.where(g > 0, g, 1.0)[:, None]), 0.0)
             o = (p8 @ v[:, h].astype(np.float64)) * (g / 255.0)[:, None]
         else:

@@ -150,22 +150,23 @@ X17_DEV void extreme_chunk(u32 const (&r)[32], u32 col0, u32 lo, u32 span, i32 (
 
 // Per-token-per-head scale mode (the benchmark description's input format; the reference has one global FixedI8
 // scale, cuda/utils_b8.cuh:7-10): value = scale[token] * code for q, k and v. The scores carry a per-key factor,
-// x = acc * a_row * k_scale[key], and V's per-key scale goes into the quantised probabilities:
-// P = rint(255 * 2^(x - m) * v_scale[key] / g), g = max over the row's keys of 2^(x - m) * v_scale[key], so that
-// P.V stays an exact u8 x s8 product and out = O * g / (255 * sum). These two helpers are the maximum sweep
-// (row maximum m of x, and of z = x + log2 v_scale) and the probability sweep of 32 columns.
-template <bool EDGE>
-X17_DEV void scaled_extreme_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 seq_len, f32 a_row, f32 const *ksc,
-								  f32 const *vsc, u32 lo, u32 span, f32 &m_loc, f32 &z_loc) {
+// x = (acc * k_scale[key]) * a_row with a_row = temperature * q_scale[row], and V's per-key scale goes into the
+// quantised probabilities: P = rint(255 * 2^(x - m) * v_scale[key] / g), g = the largest v_scale among the row's
+// visible keys, so that P <= 255, P.V stays an exact u8 x s8 product and out = O * g / (255 * sum).
+// The first sweep reduces t = acc * k_scale[key] (the row maximum of x is a_row times its largest, or for a negative
+// temperature its smallest, value) and v_scale; the second computes the probabilities of 32 columns.
+template <bool EDGE, bool WANT_MAX>
+X17_DEV void scaled_extreme_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 seq_len, f32 const *ksc, f32 const *vsc,
+								  u32 lo, u32 span, f32 &t_ext, f32 &v_max) {
 #pragma unroll
 	for (u32 i = 0; i < 32; ++i) {
 		u32 const key = key0 + i;
 		bool vis = key < seq_len;
 		if constexpr (EDGE) vis = vis && (col0 + i - lo) < span;
 		if (vis) {
-			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[i])), a_row), __ldg(ksc + key));
-			m_loc = fmaxf(m_loc, x);
-			z_loc = fmaxf(z_loc, __fadd_rn(x, lg2_approx(__ldg(vsc + key))));
+			f32 const t = __fmul_rn(__int2float_rn(i32(r[i])), __ldg(ksc + key));
+			t_ext = WANT_MAX ? fmaxf(t_ext, t) : fminf(t_ext, t);
+			v_max = fmaxf(v_max, __ldg(vsc + key));
 		}
 	}
 }
@@ -184,8 +185,8 @@ X17_DEV void scaled_softmax_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 se
 			if constexpr (EDGE) vis = vis && (col0 + i - lo) < span;
 			f32 pq = 0.0f;
 			if (vis) {
-				f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[i])), a_row), __ldg(ksc + key));
-				f32 const e = ex2_approx(__fadd_rn(x, neg_m));
+				f32 const t = __fmul_rn(__int2float_rn(i32(r[i])), __ldg(ksc + key));
+				f32 const e = ex2_approx(__fmaf_rn(t, a_row, neg_m));
 				sum = __fadd_rn(sum, e);
 				pq = fminf(__fmul_rn(__fmul_rn(e, __ldg(vsc + key)), rg), 255.0f);
 			}
@@ -199,45 +200,65 @@ X17_DEV void scaled_softmax_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 se
 
 // The same two helpers for a tile that every row sees whole and whose scale vectors can be read four keys at a
 // time (16-byte aligned: seq_len a multiple of 4): no masks, no bounds checks (the tile lies below the diagonal,
-// so its keys exist), a quarter of the loads; the arithmetic and its order are those of the general helpers.
-X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 a_row, f32 const *ksc, f32 const *vsc, f32 &m_loc,
-									   f32 &z_loc) {
+// so its keys exist), a quarter of the loads, and the multiplications and additions as packed f32x2 instructions;
+// the values are those of the general helpers (the same operations in the same order per element).
+template <bool WANT_MAX>
+X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 const *ksc, f32 const *vsc, f32 &t_ext, f32 &v_max) {
 #pragma unroll
 	for (u32 g = 0; g < 8; ++g) {
 		float4 const k4 = __ldg(reinterpret_cast<float4 const *>(ksc) + g);
 		float4 const v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
-		f32 const kf[4] = {k4.x, k4.y, k4.z, k4.w};
-		f32 const vf[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-		for (u32 e4 = 0; e4 < 4; ++e4) {
-			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[4 * g + e4])), a_row), kf[e4]);
-			m_loc = fmaxf(m_loc, x);
-			z_loc = fmaxf(z_loc, __fadd_rn(x, lg2_approx(vf[e4])));
+		f32 t0, t1, t2, t3;
+		unpack_f32x2(mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g])), __int2float_rn(i32(r[4 * g + 1]))),
+							   pack_f32x2(k4.x, k4.y)), t0, t1);
+		unpack_f32x2(mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g + 2])), __int2float_rn(i32(r[4 * g + 3]))),
+							   pack_f32x2(k4.z, k4.w)), t2, t3);
+		if constexpr (WANT_MAX) {
+			t_ext = fmaxf(fmaxf(t_ext, t0), t1);
+			t_ext = fmaxf(fmaxf(t_ext, t2), t3);
+		} else {
+			t_ext = fminf(fminf(t_ext, t0), t1);
+			t_ext = fminf(fminf(t_ext, t2), t3);
 		}
+		v_max = fmaxf(fmaxf(v_max, v4.x), v4.y);
+		v_max = fmaxf(fmaxf(v_max, v4.z), v4.w);
 	}
 }
 X17_DEV void scaled_softmax_chunk_full(u32 const (&r)[32], f32 a_row, f32 const *ksc, f32 const *vsc, f32 neg_m, f32 rg,
 									   f32 &sum, u32 (&pk)[8]) {
 	using namespace attn_cfg;
+	u64 const arow2 = pack_f32x2(a_row, a_row);
+	u64 const negm2 = pack_f32x2(neg_m, neg_m);
+	u64 const rg2 = pack_f32x2(rg, rg);
+	u64 const magic2 = pack_f32x2(MAGIC, MAGIC);
+	u64 sum2 = pack_f32x2(sum, 0.0f);
 #pragma unroll
 	for (u32 g = 0; g < 8; ++g) {
 		float4 const k4 = __ldg(reinterpret_cast<float4 const *>(ksc) + g);
 		float4 const v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
-		f32 const kf[4] = {k4.x, k4.y, k4.z, k4.w};
-		f32 const vf[4] = {v4.x, v4.y, v4.z, v4.w};
 		u32 q4[4];
 #pragma unroll
-		for (u32 e4 = 0; e4 < 4; ++e4) {
-			f32 const x = __fmul_rn(__fmul_rn(__int2float_rn(i32(r[4 * g + e4])), a_row), kf[e4]);
-			f32 const e = ex2_approx(__fadd_rn(x, neg_m));
-			sum = __fadd_rn(sum, e);
-			f32 const pq = fminf(__fmul_rn(__fmul_rn(e, vf[e4]), rg), 255.0f);
-			q4[e4] = __float_as_uint(__fadd_rn(pq, MAGIC));   // rint(pq) in the low byte
+		for (u32 h = 0; h < 2; ++h) {
+			u64 const kk = h == 0 ? pack_f32x2(k4.x, k4.y) : pack_f32x2(k4.z, k4.w);
+			u64 const vv = h == 0 ? pack_f32x2(v4.x, v4.y) : pack_f32x2(v4.z, v4.w);
+			u64 const t2 = mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g + 2 * h])), __int2float_rn(i32(r[4 * g + 2 * h + 1]))), kk);
+			f32 x0, x1;
+			unpack_f32x2(fma_f32x2(t2, arow2, negm2), x0, x1);
+			u64 const e2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+			sum2 = add_f32x2(sum2, e2);
+			// e * v_scale * (255 / g) <= 255 up to rounding, so no clamp: rint lands in the low mantissa byte
+			f32 qa, qb;
+			unpack_f32x2(fma_f32x2(mul_f32x2(e2, vv), rg2, magic2), qa, qb);
+			q4[2 * h] = __float_as_uint(qa);
+			q4[2 * h + 1] = __float_as_uint(qb);
 		}
 		u32 const lo2 = __byte_perm(q4[0], q4[1], 0x0040);
 		u32 const hi2 = __byte_perm(q4[2], q4[3], 0x0040);
 		pk[g] = __byte_perm(lo2, hi2, 0x5410);
 	}
+	f32 s0, s1;
+	unpack_f32x2(sum2, s0, s1);
+	sum = __fadd_rn(s0, s1);
 }
 
 // FP8PV: P.V on the fp8 tensor path (P as e4m3 of 256 * p, V as e4m3 with a per-head f32 scale, f32
@@ -502,7 +523,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 		i32 ext[4];
 #pragma unroll
 		for (u32 i = 0; i < 4; ++i) ext[i] = pos_t ? INT32_MIN : INT32_MAX;
-		f32 m_loc = -INFINITY, z_loc = -INFINITY;  // per-token-scale mode
+		f32 t_ext = pos_t ? -INFINITY : INFINITY, v_max = 0.0f;  // per-token-scale mode: extreme of acc * k_scale, largest v_scale
 		#pragma unroll 1
 		for (u32 t = t_begin; t <= t_end && ok; ++t) {
 			u32 const b = (t - t_begin) & 1u;
@@ -526,15 +547,29 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tc_fence_before();
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
 			if constexpr (SCALED) {
+				u32 const kc = k0 + col_base;
 				if (edge) {
-					scaled_extreme_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
-					scaled_extreme_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+					if (pos_t) {
+						scaled_extreme_chunk<true, true>(r0, col_base, kc, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+						scaled_extreme_chunk<true, true>(r1, col_base + 32, kc + 32, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+					} else {
+						scaled_extreme_chunk<true, false>(r0, col_base, kc, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+						scaled_extreme_chunk<true, false>(r1, col_base + 32, kc + 32, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+					}
 				} else if (scales_by_four) {
-					scaled_extreme_chunk_full(r0, a_row, ksc + k0 + col_base, vsc + k0 + col_base, m_loc, z_loc);
-					scaled_extreme_chunk_full(r1, a_row, ksc + k0 + col_base + 32, vsc + k0 + col_base + 32, m_loc, z_loc);
+					if (pos_t) {
+						scaled_extreme_chunk_full<true>(r0, ksc + kc, vsc + kc, t_ext, v_max);
+						scaled_extreme_chunk_full<true>(r1, ksc + kc + 32, vsc + kc + 32, t_ext, v_max);
+					} else {
+						scaled_extreme_chunk_full<false>(r0, ksc + kc, vsc + kc, t_ext, v_max);
+						scaled_extreme_chunk_full<false>(r1, ksc + kc + 32, vsc + kc + 32, t_ext, v_max);
+					}
+				} else if (pos_t) {
+					scaled_extreme_chunk<false, true>(r0, col_base, kc, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+					scaled_extreme_chunk<false, true>(r1, col_base + 32, kc + 32, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
 				} else {
-					scaled_extreme_chunk<false>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
-					scaled_extreme_chunk<false>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, lo, span, m_loc, z_loc);
+					scaled_extreme_chunk<false, false>(r0, col_base, kc, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
+					scaled_extreme_chunk<false, false>(r1, col_base + 32, kc + 32, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
 				}
 			} else if (!edge) {
 				if (pos_t) {
@@ -572,7 +607,7 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 								: min(min(ext[0], ext[1]), min(ext[2], ext[3]));
 			if (e != (pos_t ? INT32_MIN : INT32_MAX)) cand = __fmul_rn(__int2float_rn(e), temp);
 		}
-		if constexpr (SCALED) cand = m_loc;
+		if constexpr (SCALED) cand = (t_ext > -INFINITY && t_ext < INFINITY) ? __fmul_rn(t_ext, a_row) : -INFINITY;
 		xchg[xid] = cand;
 		named_barrier_sync(1, ROW_THREADS);   // also: sks has been written
 		// sink score: exact int32 dot product of this row's q with sink_k (the sink key and value are FixedI8,
@@ -599,17 +634,14 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 								  : __fmul_rn(__int2float_rn(sink_dot), temp);
 		f32 const m = fmaxf(sink_s, fmaxf(cand, xchg[xpartner]));
 		named_barrier_sync(1, ROW_THREADS);  // the exchange area is reused for the sums
-		// per-token-scale mode: g = 2^(mz - m), the largest 2^(x - m) * v_scale of the row; P = 255 * (...) / g
+		// per-token-scale mode: g = the row's largest v_scale; P = 255 * 2^(x - m) * v_scale / g
 		f32 g_row = 0.0f, rg = 0.0f;
 		if constexpr (SCALED) {
-			xchg[xid] = z_loc;
+			xchg[xid] = v_max;
 			named_barrier_sync(1, ROW_THREADS);
-			f32 const mz = fmaxf(z_loc, xchg[xpartner]);
+			g_row = fmaxf(v_max, xchg[xpartner]);   // the largest v_scale among the row's visible keys
 			named_barrier_sync(1, ROW_THREADS);
-			if (mz > -INFINITY) {
-				g_row = ex2_approx(__fsub_rn(mz, m));
-				rg = __fmul_rn(255.0f, ex2_approx(__fsub_rn(m, mz)));
-			}
+			if (g_row > 0.0f) rg = __fmul_rn(255.0f, rcp_approx(g_row));
 		}
 
 		// ---- sweep 2: probabilities against the final maximum ----
