@@ -1115,6 +1115,30 @@ class Runner:
             self.dist.all_reduce(total, op=self.dist.ReduceOp.MAX)
         return float(total[0]), float(np.mean(dev_times)), float(total[1]), int(launches), clocks
 
+    def time_burst(self, step, steps, idle_s=1.0):
+        """The same step timed the way a kernel is timed alone: the GPU idles for `idle_s`, three untimed steps bring
+        the clocks up, then `steps` steps are timed with device events (N = 1 only). Returns (seconds per step,
+        clock record): the burst counterpart of `time_steps`, whose timed region follows half a second of load."""
+        self.stream.synchronize()
+        time.sleep(idle_s)
+        for _ in range(3):
+            step()
+        self.stream.synchronize()
+        sampler = ClockSampler(self.local)
+        sampler.start()
+        tm = self.device.CudaTimer(self.stream)
+        wall0 = time.time()
+        tm.start()
+        for _ in range(steps):
+            step()
+        tm.stop()
+        self.stream.synchronize()
+        wall1 = time.time()
+        clocks = sampler.stop(wall0, wall1)
+        per = tm.elapsed_seconds() / steps
+        tm.destroy()
+        return per, clocks
+
     def steps_for(self, step, seconds, lo=3, hi=100000):
         """How many steps fill `seconds` of device time (measured on three)."""
         tm = self.device.CudaTimer(self.stream)
@@ -1229,6 +1253,16 @@ def main():
     value = work_job * args.steps / dev_total / scale
     achieved = work_rank / kernel_avg / scale
 
+    # ---- the same step as a burst: after an idle second, without the load in front of the timed region ----
+    burst = None
+    if world == 1:
+        n_burst = max(3, min(args.steps, 20))
+        per, bclk = run.time_burst(w.step, n_burst)
+        burst = {"value": work_job / per / scale, "unit": unit, "ms_per_step": per * 1e3, "steps": n_burst, "clocks": bclk,
+                 "note": "three untimed steps after an idle second, then the timed steps: the condition of the burst peak"}
+        if w.bound == "tensor":
+            burst["frac_of_burst"] = burst["value"] / (2.0 * peaks["bf16_burst"])
+
     # ---- the same step with the outputs gathered on every GPU ----
     gather = None
     if strong and world > 1 and not args.no_gather:
@@ -1287,6 +1321,8 @@ def main():
         "wall_ms_per_step": wall_total / args.steps * 1e3,
         "attn_schedule": args.attn_schedule, "gemm_tiling": args.gemm_tiling,
     }
+    if burst is not None:
+        line["burst"] = burst
     if gather is not None:
         line["gather"] = gather
     if args.workload in ("attn", "attn_pv_fp8", "attn_scaled"):
