@@ -289,8 +289,27 @@ class AttnPrefill:
         self.chunk_l = t.empty(hb, self.S, dtype=t.float32, device=self.out.device)
         self.chunk_gathered = [t.empty((world, self.S, hb * self.D), dtype=t.int8, device=self.out.device) for _ in self.chunks]
         self.chunk_events = [t.cuda.Event() for _ in self.chunks]
+        # third form: no gather pass at all, the kernel's epilogue stores each shard on every GPU (peer stores)
+        self.peers = None
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings are all this needs
+            from x17ai_b200 import sharding
+            import torch.distributed as dist
+            self.peers = sharding.PeerOutputs(self.B, self.H, self.D, self.S, world, dist.get_rank(), self.out.device)
+            self.peer_kern = K.AttnKernel(K.AttnKernelConfig(self.nh, self.D, self.H * self.D, 2 * self.H * self.D, self.peers.cols))
+            self.peer_note = "ok"
+        except Exception as e:   # symmetric memory unavailable: the line says so and carries the two NCCL forms
+            self.peers, self.peer_note = None, f"{type(e).__name__}: {str(e)[:160]}"
         return {"chunks": len(self.chunks), "heads_per_chunk": hb,
                 "layout": "gathered[chunk][rank][seq][heads_per_chunk * head_dim]"}
+
+    def step_peer_stores(self):
+        """The kernel writes its shard into every GPU's buffer; a device-side barrier between the ranks closes the step
+        (when it has passed, every rank's launch of this step has completed and every buffer holds every shard)."""
+        self.peer_kern.launch_head_block(self.stream, self.q, self.kv, self.sink_k, self.sink_v, self.temp, self.peers.out,
+                                         self.l, self.W, self.shard.head_begin, peer_outs=self.peers.peer_outs)
+        with self.torch.cuda.stream(self.ext):
+            self.peers.barrier()
 
     def step_gather(self):
         import torch.distributed as dist
@@ -1275,6 +1294,14 @@ def main():
                       ms_per_step_gather_overlapped=o_total / n * 1e3, value_gather_overlapped=work_job * n / o_total / scale,
                       note="all_gather_into_tensor (NCCL) of the int8 outputs: once after the kernel; and per chunk on a "
                            "second stream under the next chunk's kernel")
+        if w.peers is not None:
+            p_total, _, _, _, _ = run.time_steps(w.step_peer_stores, n, 3)
+            gather.update(ms_per_step_peer_stores=p_total / n * 1e3, value_peer_stores=work_job * n / p_total / scale,
+                          peer_stores="the kernel's epilogue stores each shard into every GPU's buffer over NVLink "
+                                      "(x17ai_b200_attn_fwd_i8_to_peers), a device-side barrier between the ranks closes "
+                                      "the step; no gather pass")
+        else:
+            gather["peer_stores"] = "not run: " + w.peer_note
 
     # ---- end to end through the C ABI with host buffers ----
     e2e = None

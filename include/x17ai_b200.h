@@ -208,6 +208,22 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(
 	float const *attn_temperature, float const *v_scale, uint16_t *out_bf16, float *l, size_t window_size);
 
 /*
+ * x17ai_b200_attn_fwd_i8 whose epilogue also stores the output into `n_peers` (at most 7) more buffers with the
+ * layout of `out`: peer-mapped addresses of other GPUs' memory (CUDA IPC, cuMemMap or symmetric-memory pointers
+ * valid in this process), written with plain 16-byte stores over NVLink as each row is finished.  One process per
+ * GPU runs its shard of the batch (x17ai_b200/sharding.py) with `out` = its slot of its own gathered buffer and
+ * `peer_out[i]` = the same slot of peer i's: when every rank's launch has completed, every GPU holds every shard,
+ * and no all-gather pass follows.  The caller orders "all launches completed" before the buffers are read (a
+ * barrier between the ranks on the stream); nothing in the kernel waits on another GPU.  Always the
+ * one-CTA-per-query-tile kernel.
+ */
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_to_peers(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, int8_t *const *peer_out,
+	size_t n_peers);
+
+/*
  * The int8 attention for inputs quantised with one symmetric f32 scale per token and head (value = scale * code,
  * scale = absmax / 127: the input format of the benchmark description) and bf16 output.  No counterpart in the
  * reference, whose tensors carry one global FixedI8 scale (cuda/utils_b8.cuh:7-10, 629-632) and whose kernel writes

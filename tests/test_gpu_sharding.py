@@ -113,3 +113,58 @@ def test_two_gpus_gather_the_single_gpu_result(B, H):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert got == [(0, True), (1, True)]
+
+
+def _rank_peer(rank, world, port, B, H, D, S, W, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    import torch.distributed as dist
+    from x17ai_b200 import device, kernels as K, sharding
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        with device.CudaStream(rank) as stream:
+            q, kv, sk, sv, temp = _inputs(B, S, H, D, dev)
+            peers = sharding.PeerOutputs(B, H, D, S, world, rank, dev)
+            peers.buf.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()                      # nobody's zero-fill may land on a peer's stores
+            sh = peers.shards[rank]
+            nh = sh.head_end - sh.head_begin
+            kern = K.AttnKernel(K.AttnKernelConfig(nh, D, H * D, 2 * H * D, peers.cols))
+            kern.launch_head_block(stream, q[sh.seq_begin:sh.seq_end], kv[sh.seq_begin:sh.seq_end], sk, sv, temp, peers.out,
+                                   None, W, sh.head_begin, peer_outs=peers.peer_outs)
+            with torch.cuda.stream(torch.cuda.ExternalStream(stream.handle)):
+                peers.barrier()                 # every rank's launch has completed
+            stream.synchronize()
+            full = peers.assemble()
+            want = torch.zeros(B, S, H * D, dtype=torch.int8, device=dev)
+            K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D)).launch(stream, q, kv, sk, sv, temp, want, None, W)
+            stream.synchronize()
+            torch.cuda.synchronize()
+            ok = bool(torch.equal(full, want)) and stream.read_status() == [0, 0, 0, 0]
+            dist.barrier()                      # nobody frees a buffer that a peer may still read or write
+        result.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B,H", [(2, 4), (1, 4), (3, 4)])
+def test_two_gpus_store_their_outputs_on_each_other(B, H):
+    """Two ranks, one GPU each: the kernel's epilogue stores every shard into both GPUs' buffers (peer stores over
+    NVLink, no gather pass); after a barrier every rank holds the bytes of the single launch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = 29700 + (os.getpid() % 1000)
+    procs = [ctx.Process(target=_rank_peer, args=(r, 2, port, B, H, 128, 384, 128, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(result.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert got == [(0, True), (1, True)]

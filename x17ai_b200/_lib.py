@@ -107,6 +107,8 @@ SIGNATURES = {
     "x17ai_cuda_launch_kernel": (DIAG, [c_void_p, c_void_p] + [c_size_t] * 7 + [POINTER(c_void_p)]),
     "x17ai_b200_attn_meta": (DIAG, [POINTER(AttnConfig), POINTER(AttnMeta)]),
     "x17ai_b200_attn_fwd_i8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7 + [c_size_t]),
+    "x17ai_b200_attn_fwd_i8_to_peers": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 7
+                                        + [c_size_t, c_void_p, c_size_t]),
     "x17ai_b200_attn_fwd_pv_fp8": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t] + [c_void_p] * 8 + [c_size_t]),
     "x17ai_b200_attn_fwd_i8_scaled": (DIAG, [c_void_p, POINTER(AttnConfig), c_size_t, c_size_t, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),

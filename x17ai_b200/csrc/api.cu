@@ -195,8 +195,18 @@ x17ai_DiagnosticBuffer *attn_launch(
 	size_t seq_len, int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
 	float const *temperature, void *out, float *l, size_t window_size, int32_t *dbg_s,
 	uint8_t *dbg_p, int32_t *dbg_o, float const *v_scale = nullptr, float const *tok_q = nullptr,
-	float const *tok_k = nullptr, float const *tok_v = nullptr) {
+	float const *tok_k = nullptr, float const *tok_v = nullptr, int8_t *const *peer_out = nullptr,
+	size_t n_peer_out = 0) {
 	if (auto *d = check_attn_config(cfg, who)) return d;
+	if (n_peer_out > x17::AttnParams::MAX_PEER_OUT || (n_peer_out > 0 && peer_out == nullptr)) {
+		return make_diag("x17ai_b200: bad peer outputs", who, ": at most ", size_t(x17::AttnParams::MAX_PEER_OUT),
+						 " peer copies of the output");
+	}
+	for (size_t i = 0; i < n_peer_out; ++i) {
+		if (peer_out[i] == nullptr || !aligned16(peer_out[i])) {
+			return make_diag("x17ai_b200: bad peer outputs", who, ": peer outputs must be non-null and 16-byte aligned");
+		}
+	}
 	if (batch == 0 || seq_len == 0) {
 		return make_diag("x17ai_b200: empty attention input", who, ": attention input q has zero size");
 	}
@@ -251,9 +261,12 @@ x17ai_DiagnosticBuffer *attn_launch(
 	p.dbg_s = dbg_s;
 	p.dbg_p = dbg_p;
 	p.dbg_o = dbg_o;
+	p.n_peer_out = uint32_t(n_peer_out);
+	for (size_t i = 0; i < n_peer_out; ++i) p.peer_out[i] = peer_out[i];
 
 	cudaError_t ce;
-	if (!SCALED && g_attn_schedule.load(std::memory_order_relaxed) == X17AI_B200_ATTN_PERSISTENT) {
+	// (peer copies are written by the one-CTA-per-tile kernel's epilogue only)
+	if (!SCALED && n_peer_out == 0 && g_attn_schedule.load(std::memory_order_relaxed) == X17AI_B200_ATTN_PERSISTENT) {
 		// items = runs of consecutive query tiles of one (batch, head), dealt round-robin to one CTA per
 		// SM. Long runs pay the unfused maximum sweep of their first tile less often; short runs
 		// balance the SMs: halve the run while fewer than two items per SM come out.
@@ -834,6 +847,16 @@ x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8(
 	float const *attn_temperature, int8_t *out, float *l, size_t window_size) {
 	return attn_launch<false>("x17ai_b200_attn_fwd_i8()", stream, cfg, batch, seq_len, q, kv, sink_k, sink_v,
 							  attn_temperature, out, l, window_size, nullptr, nullptr, nullptr);
+}
+
+x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_i8_to_peers(
+	x17ai_CudaStreamHandle *stream, x17ai_AttnConfig const *cfg, size_t batch, size_t seq_len,
+	int8_t const *q, int8_t const *kv, int8_t const *sink_k, int8_t const *sink_v,
+	float const *attn_temperature, int8_t *out, float *l, size_t window_size, int8_t *const *peer_out,
+	size_t n_peers) {
+	return attn_launch<false>("x17ai_b200_attn_fwd_i8_to_peers()", stream, cfg, batch, seq_len, q, kv, sink_k, sink_v,
+							  attn_temperature, out, l, window_size, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+							  nullptr, peer_out, n_peers);
 }
 
 x17ai_DiagnosticBuffer *x17ai_b200_attn_fwd_pv_fp8(

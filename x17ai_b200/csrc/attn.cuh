@@ -41,6 +41,12 @@ struct AttnParams {
 	f32 const *temperature;
 	void *out;  // int8 FixedI8, or bf16 in the fp8 P.V mode
 	u64 o_stride, o_batch_stride;  // in elements of the output type
+	// FixedI8 output only: copies of `out` in other GPUs' memory (peer-mapped addresses of buffers with the layout of
+	// `out`); the epilogue stores every 16 bytes it writes there as well, so a gather of the shards' outputs costs
+	// no pass of its own
+	static constexpr u32 MAX_PEER_OUT = 7;
+	u32 n_peer_out;
+	i8 *peer_out[MAX_PEER_OUT];
 	f32 const *v_scale;  // fp8 P.V mode: per-head scale of the e4m3 V values
 	// per-token-per-head scale mode: value = scale * code, [batch][head][seq] f32 each (null otherwise)
 	f32 const *tok_q_scale, *tok_k_scale, *tok_v_scale;
@@ -71,6 +77,11 @@ constexpr f32 MAGIC = 12582912.0f;  // 1.5 * 2^23
 constexpr u32 MAGIC_BITS = 0x4B400000u;
 }  // namespace attn_cfg
 
+X17_DEV uint4 ld_shared_v4(u32 addr) {
+	uint4 v;
+	asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+	return v;
+}
 X17_DEV void st_shared_v4(u32 addr, u32 a, u32 b, u32 c, u32 d) {
 	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
 				 : "memory");
@@ -789,7 +800,12 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 						u32 const hi2 = __byte_perm(b4[2], b4[3], 0x0040);
 						pk[g] = __byte_perm(lo2, hi2, 0x5410);
 					}
-					if (row_ok) {
+					if (p.n_peer_out != 0) {
+						// the tile is collected row-major in the P buffer (free: the last P.V has completed), 16-byte
+						// chunks XOR-swizzled by the row, and stored below in whole rows
+						u32 const ch = (d0 + c) >> 4;
+						st_shared_v4(s_p + row * D + ((ch ^ (row & (D / 16 - 1))) << 4), pk[0], pk[1], pk[2], pk[3]);
+					} else if (row_ok) {
 						*reinterpret_cast<uint4 *>(static_cast<i8 *>(p.out) + out_off + c) =
 							make_uint4(pk[0], pk[1], pk[2], pk[3]);
 						if constexpr (DEBUG) {
@@ -803,6 +819,28 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			if (row_ok && half == 0 && p.l != nullptr) {
 				p.l[u64(batch) * p.l_batch_stride + u64(head) * p.seq_len + qi] =
 					__fadd_rn(lg2_approx(total), m);
+			}
+		}
+		// Output copies in other GPUs' memory: the rows of the tile leave shared memory whole (eight lanes per 128-byte
+		// row of a head), to this GPU's `out` and to every peer's copy with plain stores over NVLink; 16-byte stores of one
+		// thread per row, as the direct path above issues them, would cross the link as 16-byte packets. Every row thread
+		// reaches this barrier, whatever its waits returned.
+		if (p.n_peer_out != 0) {
+			if constexpr (!FP8PV && !SCALED) {
+				named_barrier_sync(1, ROW_THREADS);
+				constexpr u32 CH = D / 16;   // 16-byte chunks per row
+				u32 const tid = threadIdx.x - 64u;
+#pragma unroll
+				for (u32 k = 0; k < (BQ * CH) / ROW_THREADS; ++k) {
+					u32 const idx = k * ROW_THREADS + tid;
+					u32 const rr = idx / CH, cc = idx % CH;
+					if (ok && q0 + rr < p.seq_len) {
+						uint4 const v = ld_shared_v4(s_p + rr * D + ((cc ^ (rr & (CH - 1))) << 4));
+						u64 const off = u64(batch) * p.o_batch_stride + u64(q0 + rr) * p.o_stride + head * D + cc * 16u;
+						*reinterpret_cast<uint4 *>(static_cast<i8 *>(p.out) + off) = v;
+						for (u32 pr = 0; pr < p.n_peer_out; ++pr) *reinterpret_cast<uint4 *>(p.peer_out[pr] + off) = v;
+					}
+				}
 			}
 		}
 	}

@@ -154,13 +154,16 @@ class AttnKernel:
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q), _ptr(kv), _ptr(sink_k), _ptr(sink_v),
             _ptr(attn_temperature), _ptr(out), _ptr(l), window_size))
 
-    def launch_head_block(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, head_begin):
+    def launch_head_block(self, stream, q, kv, sink_k, sink_v, attn_temperature, out, l, window_size, head_begin,
+                          peer_outs=()):
         """A head-sharded launch: this kernel's `n_heads` heads starting at head `head_begin` of wider tensors.
         The reference kernel addresses a head group the same way, by column offset with explicit row strides
         (cuda/attn_fwd_i8.cuh:378-384). `q` [.., S, q_stride] and `kv` [.., S, kv_stride] are the full-width
         tensors of all heads, `sink_k` / `sink_v` [H_total, D] and `attn_temperature` [H_total] those of all
         heads; `out` [.., S, o_stride] and `l` [.., n_heads, S] belong to this block alone (column 0 of `out`
-        is the block's first head)."""
+        is the block's first head). `peer_outs`: up to seven device addresses (int) of buffers with the layout of
+        `out` in other GPUs' memory, mapped into this process; the kernel's epilogue stores the output there as
+        well (x17ai_b200_attn_fwd_i8_to_peers), which replaces an all-gather of the shards' outputs."""
         c = self.config
         batch = q.shape[0] if q.dim() == 3 else 1
         q2, kv2, out2 = (q[0], kv[0], out[0]) if q.dim() == 3 else (q, kv, out)
@@ -182,6 +185,15 @@ class AttnKernel:
                 raise X17Error("attention batched inputs must be contiguous")
         cfg = c._c()
         hb, d = head_begin, c.head_dim
+        if peer_outs:
+            if len(peer_outs) > 7:
+                raise X17Error("attention output can be copied to at most seven peers")
+            arr = (ctypes.c_void_p * len(peer_outs))(*[int(a) for a in peer_outs])
+            check(self._lib.x17ai_b200_attn_fwd_i8_to_peers(
+                stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q) + hb * d, _ptr(kv) + 2 * hb * d,
+                _ptr(sink_k) + hb * d, _ptr(sink_v) + hb * d, _ptr(attn_temperature) + 4 * hb, _ptr(out), _ptr(l),
+                window_size, ctypes.cast(arr, ctypes.c_void_p), len(peer_outs)))
+            return
         check(self._lib.x17ai_b200_attn_fwd_i8(
             stream.handle, ctypes.byref(cfg), batch, seq_len, _ptr(q) + hb * d, _ptr(kv) + 2 * hb * d,
             _ptr(sink_k) + hb * d, _ptr(sink_v) + hb * d, _ptr(attn_temperature) + 4 * hb, _ptr(out), _ptr(l),

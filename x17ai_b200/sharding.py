@@ -9,9 +9,10 @@ are independent, so the units of work are independent:
                        of a sequence are split into contiguous column blocks
   GEMM / RMSNorm     : contiguous token-row blocks, rounded to the M tile; weights replicated
 
-No data moves between ranks inside the path. `gather_rows` / `gather_heads` collect outputs on
+No data moves between ranks inside the path. `gather_rows` / `gather_attn` collect outputs on
 every rank (torch.distributed all_gather: NCCL on GPUs, gloo in the CPU tests) for a consumer that
-wants the whole tensor.
+wants the whole tensor; `PeerOutputs` has the attention kernel's epilogue store every shard into
+every GPU's buffer instead (peer stores over NVLink), so that no gather pass follows.
 """
 from dataclasses import dataclass
 
@@ -91,3 +92,44 @@ def gather_attn(local, batch: int, n_heads: int, head_dim: int, world: int, grou
         nb, nc = sh.seq_end - sh.seq_begin, (sh.head_end - sh.head_begin) * head_dim
         out[sh.seq_begin:sh.seq_end, :, sh.head_begin * head_dim:sh.head_end * head_dim] = p[:nb, :, :nc]
     return out
+
+
+class PeerOutputs:
+    """Every rank's attention output on every GPU without a gather pass: one buffer per GPU with a slot per rank
+    ([world, seqs, S, cols], slots padded to the largest shard), allocated as symmetric memory so that each process
+    holds the peers' buffers mapped at addresses of its own. A rank launches its shard with `out` = its slot of its
+    own buffer and `peer_outs` = the same slot of every peer's (AttnKernel.launch_head_block): the kernel's epilogue
+    writes each 16 bytes to all of them. `barrier()` (a device-side barrier between the ranks on the current torch
+    stream) orders every rank's launch before anyone reads; `assemble()` is the [batch, S, H * D] view of it."""
+
+    def __init__(self, batch: int, n_heads: int, head_dim: int, seq_len: int, world: int, rank: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        if world > 8:
+            raise ValueError("peer outputs are for the GPUs of one box (at most 8)")
+        self.batch, self.n_heads, self.head_dim, self.seq_len, self.world, self.rank = batch, n_heads, head_dim, seq_len, world, rank
+        self.shards = [attn_shard(batch, n_heads, world, r) for r in range(world)]
+        self.seqs = max(sh.seq_end - sh.seq_begin for sh in self.shards)
+        self.cols = max(sh.head_end - sh.head_begin for sh in self.shards) * head_dim
+        group = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty((world, self.seqs, seq_len, self.cols), dtype=torch.int8, device=device)
+        self.handle = symm.rendezvous(self.buf, group)
+        slot_bytes = self.seqs * seq_len * self.cols
+        sh = self.shards[rank]
+        # this rank's slot: in its own buffer (the kernel's `out`, row stride `cols`) and in every peer's
+        self.out = self.buf[rank, : sh.seq_end - sh.seq_begin]
+        self.peer_outs = [int(ptr) + rank * slot_bytes for r, ptr in enumerate(self.handle.buffer_ptrs) if r != rank]
+
+    def barrier(self, timeout_ms: int = 10000):
+        """Device-side barrier between the ranks on the current torch stream; it gives up after `timeout_ms`
+        (a rank that never arrives must not leave the others' GPUs waiting)."""
+        self.handle.barrier(0, int(timeout_ms))
+
+    def assemble(self):
+        import torch
+        out = torch.empty((self.batch, self.seq_len, self.n_heads * self.head_dim), dtype=torch.int8, device=self.buf.device)
+        for r, sh in enumerate(self.shards):
+            nb, nc = sh.seq_end - sh.seq_begin, (sh.head_end - sh.head_begin) * self.head_dim
+            out[sh.seq_begin:sh.seq_end, :, sh.head_begin * self.head_dim:sh.head_end * self.head_dim] = self.buf[r, :nb, :, :nc]
+        return out
