@@ -981,6 +981,9 @@ METRICS = {"attn": "int8 sliding-window attention prefill throughput",
            "block": "quantized block forward throughput"}
 # the other kernels of the path, reported beside the headline at N = 1 (smaller than the headline's own case
 # only where the full one would not fit the few minutes the default run has)
+# token-row workloads that --gpus N cuts into one row block per GPU (strong scaling): name -> default --shape
+ROW_SHARDED = {"ffn_i8": (16384, 4096, 14336), "ffn_f8": (16384, 4096, 14336), "ffn_e4m3": (16384, 4096, 14336),
+               "qkvg": (16384, 4096, 32, 128)}
 SIDE_WORKLOADS = ["ffn_i8", "ffn_f8", "ffn_e4m3", "qkvg", "attn_pv_fp8", "attn_scaled", "decode", "rms_norm", "block"]
 
 
@@ -1038,7 +1041,7 @@ def run_reference(args, rank, world):
     v = float(np.mean(vals)) / scale
     line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-            "scaling": "strong" if args.workload == "attn" else "weak",
+            "scaling": "strong" if args.workload == "attn" or (args.workload in ROW_SHARDED and world > 1) else "weak",
             "vs_baseline": None, "dtype": "f32/int (numpy)", "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -1247,10 +1250,24 @@ def main():
     K.set_gemm_tiling(K.GEMM_CTA_PAIR if args.gemm_tiling == "cta_pair" else K.GEMM_ONE_CTA)
     run = Runner(torch, dist, lib, device, stream, local, world, dev)
     strong = args.workload == "attn"
+    row_sharded = args.workload in ROW_SHARDED and world > 1
     if strong:
         B, H = (_shape(args, 5) or (8, 32, 0, 0, 0))[:2]
         shard = sharding.attn_shard(B, H, world, rank)
         w = WORKLOADS["attn"](stream, dev, args, shard=shard)
+    elif row_sharded:
+        # the fixed token rows of the workload cut into one block per GPU (whole M tiles), weights replicated
+        import types
+        fields = list(_shape(args, len(ROW_SHARDED[args.workload])) or ROW_SHARDED[args.workload])
+        rows_total = fields[0]
+        b, e = sharding.row_shard(rows_total, world, rank)
+        if e <= b:
+            raise SystemExit(f"{args.workload}: {rows_total} token rows are too few for {world} GPUs")
+        fields[0] = e - b
+        w = WORKLOADS[args.workload](stream, dev, types.SimpleNamespace(shape=",".join(str(v) for v in fields)))
+        w.ops_total = w.ops / (e - b) * rows_total
+        w.tokens_total = rows_total
+        strong = True
     else:
         w = WORKLOADS[args.workload](stream, dev, args)
     if args.sequential:
@@ -1284,7 +1301,7 @@ def main():
 
     # ---- the same step with the outputs gathered on every GPU ----
     gather = None
-    if strong and world > 1 and not args.no_gather:
+    if args.workload == "attn" and world > 1 and not args.no_gather:
         info = w.gather_setup(world)
         n = max(5, min(args.steps, 50))
         g_total, _, _, _, _ = run.time_steps(w.step_gather, n, 3)
@@ -1338,7 +1355,9 @@ def main():
         "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic (seeded N(0,1) values quantised to FixedI8 codes)",
         "config": dict(w.config, sharding=(
-            f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path"
+            (f"the fixed {w.tokens_total} token rows cut into {world} blocks of whole M tiles, one per GPU, weights replicated, "
+             "no collective in the path" if row_sharded else
+             f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path")
             if strong else f"{world} x per-GPU workload, token-row units, no collective"),
             load_before_timed_region=f"{PRELOAD_S} s of the same step after the warm-up steps, back to back"),
         "tokens_per_s": tokens_job * args.steps / dev_total,
