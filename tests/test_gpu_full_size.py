@@ -103,6 +103,38 @@ def test_attention_pv_fp8_full_size(stream):
     assert torch.equal(out1[0], out[5])
 
 
+def test_attention_per_token_scales_full_size(stream):
+    """The per-token-scale mode at configs[1]'s size through two properties that need no oracle at that size: with
+    every scale 1/8 it is the FixedI8 kernel (out = code / 8 to half a code and bf16 precision, L equal), and
+    doubling every query scale of a sequence while halving its temperature changes nothing."""
+    from x17ai_b200 import kernels as K
+    B, H, D, S, W = 8, 32, 128, 8192, 1024
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, kv, sk, sv = _codes(g, B, S, H * D), _codes(g, B, S, 2 * H * D), _codes(g, H, D), _codes(g, H, D)
+    temp = (0.5 + torch.rand(H, generator=g, device="cuda")).float()
+    kern = K.AttnKernel(K.AttnKernelConfig(H, D, H * D, 2 * H * D, H * D))
+    out_i8 = torch.zeros(B, S, H * D, dtype=torch.int8, device="cuda")
+    l_i8 = torch.zeros(B, H, S, dtype=torch.float32, device="cuda")
+    eighth = torch.full((B, H, S), 0.125, dtype=torch.float32, device="cuda")
+    out = torch.zeros(B, S, H * D, dtype=torch.bfloat16, device="cuda")
+    l = torch.zeros(B, H, S, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    kern.launch(stream, q, kv, sk, sv, temp, out_i8, l_i8, W)
+    kern.launch_scaled(stream, q, eighth, kv, eighth, eighth, sk, sv, temp, out, l, W)
+    stream.synchronize()
+    want = out_i8.float() / 8.0
+    diff = (out.float() - want).abs().max().item()
+    assert diff <= 0.5 / 8 + 2.0 ** -8 * want.abs().max().item() + 1e-3, diff
+    assert (l - l_i8).abs().max().item() <= 1e-3
+    # scale invariance: q_scale * 2 with temperature / 2 is the same attention (powers of two: exact in f32)
+    out2 = torch.zeros_like(out)
+    torch.cuda.synchronize()
+    kern.launch_scaled(stream, q, eighth * 2.0, kv, eighth, eighth, sk, sv, temp * 0.5, out2, None, W)
+    stream.synchronize()
+    assert stream.read_status() == [0, 0, 0, 0]
+    assert torch.equal(out2, out)      # the row factor temperature * q_scale is the same float
+
+
 def test_ffn_full_size(stream):
     """configs[3]: 16384 tokens, d_model 4096, hidden 14336: GeGLU GEMM and the e4m3 x int8 projection with the
     gated residual, sampled token rows against the oracle (rows are independent units)."""
