@@ -213,17 +213,26 @@ X17_DEV void scaled_softmax_chunk(u32 const (&r)[32], u32 col0, u32 key0, u32 se
 // time (16-byte aligned: seq_len a multiple of 4): no masks, no bounds checks (the tile lies below the diagonal,
 // so its keys exist), a quarter of the loads, and the multiplications and additions as packed f32x2 instructions;
 // the values are those of the general helpers (the same operations in the same order per element).
-template <bool WANT_MAX>
-X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 const *ksc, f32 const *vsc, f32 &t_ext, f32 &v_max) {
+// EDGE: the tile lies inside the sequence but the row sees only columns lo <= col < lo + span of it
+template <bool WANT_MAX, bool EDGE = false>
+X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 const *ksc, f32 const *vsc, f32 &t_ext, f32 &v_max,
+									   u32 col0 = 0, u32 lo = 0, u32 span = 0) {
 #pragma unroll
 	for (u32 g = 0; g < 8; ++g) {
 		float4 const k4 = __ldg(reinterpret_cast<float4 const *>(ksc) + g);
-		float4 const v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
+		float4 v4 = __ldg(reinterpret_cast<float4 const *>(vsc) + g);
 		f32 t0, t1, t2, t3;
 		unpack_f32x2(mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g])), __int2float_rn(i32(r[4 * g + 1]))),
 							   pack_f32x2(k4.x, k4.y)), t0, t1);
 		unpack_f32x2(mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g + 2])), __int2float_rn(i32(r[4 * g + 3]))),
 							   pack_f32x2(k4.z, k4.w)), t2, t3);
+		if constexpr (EDGE) {
+			f32 const none = WANT_MAX ? -INFINITY : INFINITY;
+			bool const s0 = (col0 + 4 * g - lo) < span, s1 = (col0 + 4 * g + 1 - lo) < span;
+			bool const s2 = (col0 + 4 * g + 2 - lo) < span, s3 = (col0 + 4 * g + 3 - lo) < span;
+			t0 = s0 ? t0 : none; t1 = s1 ? t1 : none; t2 = s2 ? t2 : none; t3 = s3 ? t3 : none;
+			v4.x = s0 ? v4.x : 0.0f; v4.y = s1 ? v4.y : 0.0f; v4.z = s2 ? v4.z : 0.0f; v4.w = s3 ? v4.w : 0.0f;
+		}
 		if constexpr (WANT_MAX) {
 			t_ext = fmaxf(fmaxf(t_ext, t0), t1);
 			t_ext = fmaxf(fmaxf(t_ext, t2), t3);
@@ -235,8 +244,9 @@ X17_DEV void scaled_extreme_chunk_full(u32 const (&r)[32], f32 const *ksc, f32 c
 		v_max = fmaxf(fmaxf(v_max, v4.z), v4.w);
 	}
 }
+template <bool EDGE = false>
 X17_DEV void scaled_softmax_chunk_full(u32 const (&r)[32], f32 a_row, f32 const *ksc, f32 const *vsc, f32 neg_m, f32 rg,
-									   f32 &sum, u32 (&pk)[8]) {
+									   f32 &sum, u32 (&pk)[8], u32 col0 = 0, u32 lo = 0, u32 span = 0) {
 	using namespace attn_cfg;
 	u64 const arow2 = pack_f32x2(a_row, a_row);
 	u64 const negm2 = pack_f32x2(neg_m, neg_m);
@@ -255,6 +265,10 @@ X17_DEV void scaled_softmax_chunk_full(u32 const (&r)[32], f32 a_row, f32 const 
 			u64 const t2 = mul_f32x2(pack_f32x2(__int2float_rn(i32(r[4 * g + 2 * h])), __int2float_rn(i32(r[4 * g + 2 * h + 1]))), kk);
 			f32 x0, x1;
 			unpack_f32x2(fma_f32x2(t2, arow2, negm2), x0, x1);
+			if constexpr (EDGE) {   // ex2(-inf) = 0: no weight, no share of the sum
+				x0 = (col0 + 4 * g + 2 * h - lo) < span ? x0 : -INFINITY;
+				x1 = (col0 + 4 * g + 2 * h + 1 - lo) < span ? x1 : -INFINITY;
+			}
 			u64 const e2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
 			sum2 = add_f32x2(sum2, e2);
 			// e * v_scale * (255 / g) <= 255 up to rounding, so no clamp: rint lands in the low mantissa byte
@@ -559,7 +573,15 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			mbar_arrive(s_done_bar(b));  // S_b is in registers now
 			if constexpr (SCALED) {
 				u32 const kc = k0 + col_base;
-				if (edge) {
+				if (edge && scales_by_four && k0 + BKV <= p.seq_len) {   // an edge tile whose keys all exist
+					if (pos_t) {
+						scaled_extreme_chunk_full<true, true>(r0, ksc + kc, vsc + kc, t_ext, v_max, col_base, lo, span);
+						scaled_extreme_chunk_full<true, true>(r1, ksc + kc + 32, vsc + kc + 32, t_ext, v_max, col_base + 32, lo, span);
+					} else {
+						scaled_extreme_chunk_full<false, true>(r0, ksc + kc, vsc + kc, t_ext, v_max, col_base, lo, span);
+						scaled_extreme_chunk_full<false, true>(r1, ksc + kc + 32, vsc + kc + 32, t_ext, v_max, col_base + 32, lo, span);
+					}
+				} else if (edge) {
 					if (pos_t) {
 						scaled_extreme_chunk<true, true>(r0, col_base, kc, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
 						scaled_extreme_chunk<true, true>(r1, col_base + 32, kc + 32, p.seq_len, ksc, vsc, lo, span, t_ext, v_max);
@@ -682,7 +704,10 @@ X17_DEV void attn_fwd_body(CUtensorMap const *tm_q_ptr, CUtensorMap const *tm_kv
 			tc_fence_before();
 			mbar_arrive(s_done_bar(0));  // S is in registers: the next Q.K^T may overwrite it
 			if constexpr (SCALED) {
-				if (edge) {
+				if (edge && scales_by_four && k0 + BKV <= p.seq_len) {
+					scaled_softmax_chunk_full<true>(r0, a_row, ksc + k0 + col_base, vsc + k0 + col_base, neg_m, rg, sum[0], pk0, col_base, lo, span);
+					scaled_softmax_chunk_full<true>(r1, a_row, ksc + k0 + col_base + 32, vsc + k0 + col_base + 32, neg_m, rg, sum[1], pk1, col_base + 32, lo, span);
+				} else if (edge) {
 					scaled_softmax_chunk<true>(r0, col_base, k0 + col_base, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[0], pk0);
 					scaled_softmax_chunk<true>(r1, col_base + 32, k0 + col_base + 32, p.seq_len, a_row, ksc, vsc, neg_m, rg, lo, span, sum[1], pk1);
 				} else if (scales_by_four) {
