@@ -53,6 +53,19 @@ def attn_ops(batch, n_heads, head_dim, seq_len, window):
     return 4.0 * batch * n_heads * head_dim * float((n + 1).sum())
 
 
+def attn_line_config(B, H, S, D, W, world):
+    """`config` of the attention line, the same in both arms (`--impl ours`, `--impl reference`): the workload, how it
+    is cut over the GPUs, and why L2 does not hold it between steps (rank 0's shard)."""
+    from x17ai_b200 import sharding
+    sh = sharding.attn_shard(B, H, world, 0)
+    nb, nh = sh.seq_end - sh.seq_begin, sh.head_end - sh.head_begin
+    alg_bytes = nb * S * nh * D * 4 + nb * nh * S * 4
+    return {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H, "seq_len": S,
+            "head_dim": D, "window": W,
+            "l2": "inputs (q+kv+out = %.0f MB per GPU) larger than the 126 MB L2" % (alg_bytes / 1e6),
+            "sharding": f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path"}
+
+
 def library_tensor_peaks(torch, dev):
     """cuBLAS int8 (torch._int_mm) and fp8 (torch._scaled_mm) dense rates at 8192^3 on this GPU, best of 10,
     measured outside every timed region: a measured denominator beside the assumed 2 x bf16."""
@@ -1007,8 +1020,7 @@ def run_reference(args, rank, world):
     if args.workload in ("attn", "attn_pv_fp8", "attn_scaled"):
         # the fp8 P.V and per-token-scale variants: the int8 restatement (same operation count) stands in
         w.S, w.D, w.W, B, H = 8192, 128, 1024, 8, 32
-        cfg = {"workload": "configs[1] int8 sliding-window attention prefill", "batch": B, "n_heads": H, "seq_len": 8192,
-               "head_dim": 128, "window": 1024}
+        cfg = attn_line_config(B, H, 8192, 128, 1024, world)
         unit, metric = "TOPS", METRICS["attn"]
     elif args.workload.startswith("ffn"):
         w.Dm, w.F = 4096, 14336
@@ -1354,12 +1366,12 @@ def main():
         "ms_per_step": dev_total / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic (seeded N(0,1) values quantised to FixedI8 codes)",
-        "config": dict(w.config, sharding=(
+        "config": attn_line_config(w.B, w.H, w.S, w.D, w.W, world) if args.workload == "attn" else dict(w.config, sharding=(
             (f"the fixed {w.tokens_total} token rows cut into {world} blocks of whole M tiles, one per GPU, weights replicated, "
              "no collective in the path" if row_sharded else
              f"the fixed batch cut into {world} shards of (sequence, head) units, one per GPU, no collective in the path")
-            if strong else f"{world} x per-GPU workload, token-row units, no collective"),
-            load_before_timed_region=f"{PRELOAD_S} s of the same step after the warm-up steps, back to back"),
+            if strong else f"{world} x per-GPU workload, token-row units, no collective")),
+        "load_before_timed_region": f"{PRELOAD_S} s of the same step after the warm-up steps, back to back",
         "tokens_per_s": tokens_job * args.steps / dev_total,
         "roofline": dict(roofline(w, achieved, dev_total, peaks, lib_peaks, args.workload, clocks), kernel_ms=kernel_avg * 1e3),
         "clocks": clocks,
