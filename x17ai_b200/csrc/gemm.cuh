@@ -13,7 +13,11 @@
 //               overlaps the main loop of tile i+1
 //   warps 2..5  epilogue: tcgen05.ld (thread = row, registers = columns), fused math, 16-byte
 //               global stores
-// Tiles are walked M-fastest so that the CTAs running together share the same B tile in L2.
+// and the same roles as a pair of CTAs on two SMs (gemm_pair_kernel, the library's default): one
+// tcgen05.mma.cta_group::2 of M 256, N 256 per K step, issued by the pair's first CTA; each CTA loads its 128 rows
+// of A and half of the tile's rows of B and runs the epilogue of its own 128 rows.
+// Tiles are walked in groups of row tiles (row tiles fastest inside a group) so that the CTAs running together
+// share their A and B rows in L2.
 #pragma once
 
 #include "ptx.cuh"
