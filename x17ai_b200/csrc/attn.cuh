@@ -24,6 +24,9 @@
 //               exp2 / quantise, P written to shared memory in the 128B-swizzled K-major
 //               layout, final normalisation and 16-byte stores
 // KV tiles wholly outside [i-W', i-1] for every row of the CTA are never loaded.
+// The sink score (q . sink_k, exact int32) is taken from the Q tile in shared memory after sweep 1. With peer outputs
+// (AttnParams::peer_out) the epilogue collects the output tile in the P buffer and stores it in whole rows to this
+// GPU's buffer and to the copies in other GPUs' memory.
 #pragma once
 
 #include "ptx.cuh"
