@@ -199,7 +199,7 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 			bool ok = true;
 			for (u32 t = cta; t < n_tiles && ok; t += n_ctas) {
 				u32 tm, tn;
-				tile_origin<PAIR ? 8 : 16>(t, tiles_m, p.tiles_n, tm, tn);
+				tile_origin<16>(t, tiles_m, p.tiles_n, tm, tn);
 				i32 const m0 = i32(tm * TILE_M + rank * BM);
 				i32 const n0 = i32(tn * BN + (PAIR ? rank * (BN / 2) : 0u));
 				for (u32 kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -289,7 +289,7 @@ X17_DEV void gemm_body(CUtensorMap const *tm_a_ptr, CUtensorMap const *tm_b_ptr,
 			u32 const buf = local_tile & 1;
 			u32 const acc_ph = (local_tile >> 1) & 1;
 			u32 tm, tn;
-			tile_origin<PAIR ? 8 : 16>(t, tiles_m, p.tiles_n, tm, tn);
+			tile_origin<16>(t, tiles_m, p.tiles_n, tm, tn);
 			u32 const m0 = tm * TILE_M + rank * BM;
 			u32 const n0 = tn * BN;
 			if (!mbar_wait_warp(acc_full_bar(buf), acc_ph, ctx, ST_WAIT_ACC_FULL, buf)) {
