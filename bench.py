@@ -924,6 +924,19 @@ class Block:
         for b in range(self.B):
             self.blk.forward(self.x[b])
 
+    def stage_times(self, rounds=5):
+        """Per-stage device times of the harness form (src/main.rs:193-255 times every launch): mean over `rounds`
+        forwards of one sequence, with the stage's operation count: {stage: {"ms", "tops"}}."""
+        acc = {}
+        for _ in range(rounds):
+            self.blk.forward(self.x[0], timed=True)
+            for k, v in self.blk.seconds.items():
+                acc[k] = acc.get(k, 0.0) + v / rounds
+        ops = dict(self.stage_ops)
+        if self.blk.fused_qkv:   # one launch does both projections; the second stage is empty
+            ops["attn_q"] = ops["attn_q"] + ops.pop("attn_kv")
+        return {k: {"ms": v * 1e3, "tops": (ops[k] / v / 1e12 if k in ops and v > 1e-6 else None)} for k, v in acc.items()}
+
     def host_buffers(self):
         t = self.torch
         self.h_x = self.x.cpu().pin_memory()
@@ -1381,6 +1394,8 @@ def main():
     }
     if burst is not None:
         line["burst"] = burst
+    if args.workload == "block" and world == 1 and not args.sequential:
+        line["stages"] = w.stage_times()
     if gather is not None:
         line["gather"] = gather
     if args.workload in ("attn", "attn_pv_fp8", "attn_scaled"):
